@@ -1,0 +1,69 @@
+"""ctypes binding of libes_b200.so (the C ABI declared in include/es_b200.h).
+
+The library is the only compute path: if it is missing it is built in-tree with nvcc, and if that is impossible
+the import fails loudly — there is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p, POINTER, c_uint32
+from pathlib import Path
+
+_LIB = None
+
+OK = 0
+BF16, FP16 = 0, 1
+
+
+class EsB200Error(RuntimeError):
+    """Raised when a C-ABI call returns a non-zero status (the analogue of the reference's TORCH_CHECK failures)."""
+
+
+def _declare(lib):
+    lib.es_b200_version.restype = c_char_p
+    lib.es_b200_strerror.restype = c_char_p
+    lib.es_b200_strerror.argtypes = [c_int]
+    lib.es_b200_last_error.restype = c_char_p
+    lib.es_b200_mxfp8_grouped_quant.restype = c_int
+    lib.es_b200_mxfp8_grouped_quant.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_int, c_int64, c_int, c_void_p]
+    lib.es_b200_grouped_mm_scratch_bytes.restype = c_size_t
+    lib.es_b200_grouped_mm_scratch_bytes.argtypes = [c_int, c_int64, c_int, c_int]
+    lib.es_b200_mxfp8_grouped_mm.restype = c_int
+    lib.es_b200_mxfp8_grouped_mm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_void_p,
+                                             c_size_t, c_void_p]
+    lib.es_b200_fp8_blockwise_grouped_mm.restype = c_int
+    lib.es_b200_fp8_blockwise_grouped_mm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                     c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
+                                                     c_size_t, c_void_p]
+    lib.es_b200_check_status.restype = c_int
+    lib.es_b200_check_status.argtypes = [c_void_p, c_void_p, POINTER(c_uint32)]
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / "lib" / "libes_b200.so"
+
+
+def load():
+    """Load (building first if needed) libes_b200.so and return the ctypes handle."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not path.exists():
+        from . import build as _build
+        _build.build()
+    if not path.exists():
+        raise ImportError(f"{path} is missing and could not be built; es_b200 has no fallback path")
+    lib = ctypes.CDLL(str(path))
+    _declare(lib)
+    _LIB = lib
+    return lib
+
+
+def check(status: int):
+    if status != OK:
+        lib = load()
+        msg = lib.es_b200_last_error().decode() or lib.es_b200_strerror(status).decode()
+        raise EsB200Error(msg)

@@ -1,0 +1,61 @@
+// Library-level entry points of the es_b200 C ABI: version, error strings, per-device property cache.
+#include <mutex>
+
+#include "common.cuh"
+
+namespace es_b200 {
+
+char* last_error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int get_device_info(DeviceInfo* out) {
+  constexpr int kMaxDevices = 64;
+  static DeviceInfo cache[kMaxDevices];
+  static bool valid[kMaxDevices] = {false};
+  static std::mutex mu;
+  int dev = 0;
+  ES_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ES_B200_ERR_INVALID_ARGUMENT, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!valid[dev]) {
+    DeviceInfo d;
+    ES_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    ES_CUDA_TRY(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    ES_CUDA_TRY(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+    cache[dev] = d;
+    valid[dev] = true;
+  }
+  *out = cache[dev];
+  if (out->cc_major != 10)
+    return fail(ES_B200_ERR_UNSUPPORTED_DEVICE, "es_b200 kernels are built for sm_100a only; device %d is sm_%d%d",
+                dev, out->cc_major, out->cc_minor);
+  return ES_B200_OK;
+}
+
+}  // namespace es_b200
+
+extern "C" const char* es_b200_version(void) { return "es_b200 0.1 (sm_100a)"; }
+
+extern "C" const char* es_b200_last_error(void) { return es_b200::last_error_buffer(); }
+
+extern "C" const char* es_b200_strerror(int code) {
+  switch (code) {
+    case ES_B200_OK: return "ok";
+    case ES_B200_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case ES_B200_ERR_CUDA: return "CUDA error";
+    case ES_B200_ERR_UNSUPPORTED_DEVICE: return "unsupported device (needs compute capability 10.x)";
+    case ES_B200_ERR_SCRATCH_TOO_SMALL: return "scratch buffer too small";
+    case ES_B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait timed out";
+    default: return "unknown error code";
+  }
+}

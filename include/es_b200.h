@@ -1,0 +1,119 @@
+/*
+ * es_b200 — C ABI of the B200 (sm_100a) MoE grouped-GEMM library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle (passed as void* so that the
+ * header needs no CUDA include), enqueues its work on that stream and returns without synchronising.  Nothing
+ * is copied to the host and no host decision depends on device data, so every call can be captured in a CUDA
+ * graph.  Return value: ES_B200_OK or an error code; es_b200_last_error() gives the message of the calling
+ * thread's last failure.
+ *
+ * The three operators replace, one for one, the operators of the reference torch extension
+ * (expert_specialization/csrc/expert_specialization.cpp:56-73).  The reference passes torch::Tensor objects;
+ * here the same tensors arrive as (pointer, extent) pairs and the shape / stride checks that the reference does
+ * with TORCH_CHECK are done by the caller-side shim (expert_specialization_moe_b200/ops.py) plus the argument
+ * checks below.
+ */
+#ifndef ES_B200_H_
+#define ES_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ES_B200_OK 0
+#define ES_B200_ERR_INVALID_ARGUMENT 1 /* bad pointer / size / alignment; nothing was launched */
+#define ES_B200_ERR_CUDA 2             /* a CUDA runtime or driver call failed */
+#define ES_B200_ERR_UNSUPPORTED_DEVICE 3 /* current device is not compute capability 10.x */
+#define ES_B200_ERR_SCRATCH_TOO_SMALL 4
+#define ES_B200_ERR_DEVICE_TIMEOUT 5   /* a bounded device-side wait gave up (reported by es_b200_check_status) */
+
+/* element types */
+#define ES_B200_BF16 0
+#define ES_B200_FP16 1
+
+/* Most experts any call accepts (the reference launches one thread per expert in a single block:
+ * es_sm100_mxfp8_blockscaled_launcher.cuh:53, es_fp8_blockwise_launcher.cuh:53). */
+#define ES_B200_MAX_EXPERTS 1024
+
+const char* es_b200_version(void);
+const char* es_b200_strerror(int code);
+const char* es_b200_last_error(void);
+
+/*
+ * MXFP8 grouped quantisation.
+ * Replaces es_sm100_mxfp8_blockscaled_grouped_quant
+ *   (expert_specialization/csrc/cuda/es_sm100_mxfp8_blockscaled_group_quant.cu:5-39, kernel in
+ *    es_sm100_mxfp8_blockscaled_group_quant.cuh:261-355; Python: expert_specialization/ops.py:40-50).
+ *
+ *   input             [num_rows, k] bf16 or fp16, row-major, k % 128 == 0, 16-byte aligned
+ *   problem_sizes     [num_experts, 3] int32 (m, n, k) per expert — only m is read, as in the reference
+ *   expert_offsets    [num_experts] int32: first row of each expert in input / quant_output
+ *   blockscale_offsets[num_experts] int32: first row of each expert in the scale tensor (cumulative
+ *                     round-up-to-128 of m)
+ *   quant_output      [num_rows, k] e4m3 codes; rows outside every expert's range are not written
+ *   scale_factor      [sf_rows, k/32] UE8M0 bytes in the SM100 swizzled layout (512-byte atoms of 128 rows x 4
+ *                     K-blocks), expert e starting at byte blockscale_offsets[e] * k/32.  sf_rows must be at least
+ *                     sum(round_up(m_e, 128)).  Rows m_e..round_up(m_e,128)-1 of each expert are written as 0.
+ * Codes and the scale bytes of valid rows are bit-identical to the reference kernel's.
+ */
+int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, const int32_t* problem_sizes,
+                                const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                void* quant_output, uint8_t* scale_factor, int num_experts, int64_t num_rows, int k,
+                                void* stream);
+
+/*
+ * Scratch requirement (bytes, device memory, 256-byte aligned) of the two grouped GEMM entry points for a call
+ * with these extents.  Replaces the per-call torch::empty scratch tensors and the CUTLASS workspace of the
+ * reference (es_sm100_mxfp8_blockscaled_launcher.cuh:163-176,140-142).  The contents need no initialisation.
+ */
+size_t es_b200_grouped_mm_scratch_bytes(int num_experts, int64_t num_rows, int n, int k);
+
+/*
+ * MXFP8 block-scaled grouped GEMM:  d[off_e + i, :] = sum_k a[off_e + i, k] 2^(sfa-127) * b[e, :, k] 2^(sfb-127)
+ * Replaces es_sm100_mxfp8_blockscaled_grouped_mm
+ *   (expert_specialization/csrc/cuda/es_sm100_mxfp8_blockscaled.cu:5-40, launcher
+ *    es_sm100_mxfp8_blockscaled_launcher.cuh:16-212, addressing es_sm100_mxfp8_blockscaled_functor.cuh:61-75;
+ *    Python: expert_specialization/ops.py:32-37).
+ *
+ *   a    [num_rows, k] e4m3, row-major                      b   [num_experts, n, k] e4m3 in memory (the reference's
+ *   sfa  swizzled UE8M0, expert e at blockscale_offsets[e]*k/32     [E, k, n] view with stride(1) == 1)
+ *   sfb  swizzled UE8M0, expert e at e*n*k/32                d   [num_rows, n] bf16 or fp16
+ *   k % 128 == 0, n % 128 == 0; a, b, d 16-byte aligned; sfa, sfb 16-byte aligned.
+ * fp32 accumulation on the tensor cores, round-to-nearest to the output type.  Rows outside every expert's range
+ * are not written.
+ */
+int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d,
+                             int out_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
+                             const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n, int k,
+                             int64_t sfa_rows, void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * FP8-blockwise grouped GEMM (fp32 scales: one per 1x128 of a, one per 128x128 of b).
+ * Replaces es_fp8_blockwise_scaled_grouped_mm
+ *   (expert_specialization/csrc/cuda/es_fp8_blockwise.cu:34-193, addressing es_fp8_blockwise_functor.cuh:57-74;
+ *    Python: expert_specialization/ops.py:4-29).
+ *
+ *   a [num_rows, k] e4m3 row-major; b [num_experts, n, k] e4m3 in memory;
+ *   scales_a [num_rows, k/128] f32 row-major; scales_b [num_experts, n/128, k/128] f32 in memory;
+ *   d [num_rows, n] bf16 or fp16.  k % 128 == 0, n % 128 == 0.
+ */
+int es_b200_fp8_blockwise_grouped_mm(const void* a, const void* b, const float* scales_a, const float* scales_b,
+                                     void* d, int out_dtype, const int32_t* problem_sizes,
+                                     const int32_t* expert_offsets, int num_experts, int64_t num_rows, int n, int k,
+                                     void* scratch, size_t scratch_bytes, void* stream);
+
+/*
+ * Device-side status word of the grouped GEMMs.  Every wait inside the kernels is bounded; a wait that gives up
+ * records a non-zero code in the first 4 bytes of `scratch` and the kernel exits cleanly.  This call copies that
+ * word to the host (synchronising `stream`) and returns ES_B200_OK or ES_B200_ERR_DEVICE_TIMEOUT.  Optional:
+ * intended for tests and debugging, never needed on the hot path.
+ */
+int es_b200_check_status(const void* scratch, void* stream, uint32_t* raw_status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ES_B200_H_ */

@@ -1,0 +1,56 @@
+"""Seeded input builders shared by the CPU and GPU tests."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import mxfp8_quant_oracle as Q
+
+
+def f32_to_bf16_bits(a):
+    b = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    return ((b + np.uint32(0x7FFF) + ((b >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def activations_bits(T, K, seed, is_bf16=True, outliers=True):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((T, K), dtype=np.float32)
+    if outliers:
+        x *= np.where(rng.random((T, K), dtype=np.float32) < 0.01, np.float32(50.0), np.float32(1.0))
+    if is_bf16:
+        return f32_to_bf16_bits(x)
+    return x.astype(np.float16).view(np.uint16)
+
+
+def bits_to_tensor(x_bits, is_bf16, device):
+    dt = torch.bfloat16 if is_bf16 else torch.float16
+    return torch.from_numpy(x_bits.view(np.int16)).to(device).view(dt)
+
+
+def run_quant_op(x_bits, is_bf16, counts, device="cuda", sf_fill=0xCD, ps_n=0):
+    """Calls the product op through ops.py -> C ABI.  Returns (codes u8 [T,K], sf flat u8, ps, eo, bo)."""
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant
+    T, K = x_bits.shape
+    ps, eo, bo, sf_rows = Q.offsets_from_counts(counts, ps_n, K)
+    x = bits_to_tensor(x_bits, is_bf16, device)
+    codes = torch.zeros((T, K), dtype=torch.uint8, device=device).view(torch.float8_e4m3fn)
+    sf = torch.full((max(sf_rows, 1), K // 32), sf_fill, dtype=torch.uint8, device=device)
+    es_sm100_mxfp8_blockscaled_grouped_quant(
+        x, torch.from_numpy(ps).to(device), torch.from_numpy(eo).to(device), torch.from_numpy(bo).to(device), codes, sf)
+    torch.cuda.synchronize()
+    return codes.view(torch.uint8).cpu().numpy(), sf.cpu().numpy().reshape(-1)[: sf_rows * (K // 32)], ps, eo, bo
+
+
+def oracle_quant(x_bits, is_bf16, counts, rcp448_bits=Q.RCP_448_BITS_DEFAULT, sf_fill=0xCD):
+    T, K = x_bits.shape
+    ps, eo, bo, sf_rows = Q.offsets_from_counts(counts, 0, K)
+    codes = np.zeros((T, K), dtype=np.uint8)
+    sf = np.full(sf_rows * (K // 32), sf_fill, dtype=np.uint8)
+    Q.grouped_quant(x_bits, is_bf16, ps, eo, bo, codes, sf, rcp448_bits)
+    return codes, sf
+
+
+def valid_sf_index(counts, bo, K):
+    idx = [int(bo[e]) * (K // 32) + Q.sf_swizzled_offsets(int(counts[e]), K).ravel()
+           for e in range(len(counts)) if counts[e] > 0]
+    return np.concatenate(idx) if idx else np.zeros(0, dtype=np.int64)
