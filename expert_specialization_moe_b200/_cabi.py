@@ -38,7 +38,7 @@ def _declare(lib):
                                                      c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                                      c_size_t, c_void_p]
     lib.es_b200_check_status.restype = c_int
-    lib.es_b200_check_status.argtypes = [c_void_p, c_void_p, POINTER(c_uint32)]
+    lib.es_b200_check_status.argtypes = [c_void_p, POINTER(c_uint32)]
 
 
 def library_path() -> Path:

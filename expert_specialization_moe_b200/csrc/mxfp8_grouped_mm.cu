@@ -1,0 +1,350 @@
+// MXFP8 block-scaled grouped GEMM for sm_100a, hand-written around tcgen05.mma.kind::mxf8f6f4.block_scale.
+//
+// Per expert e:  d[off_e + i, n] = sum_k a[off_e + i, k] * 2^(sfa-127) * b[e, n, k] * 2^(sfb-127), fp32 accumulate.
+//
+// Mapping ("swap-AB"): the 128 rows of the tensor-core tile are 128 WEIGHT rows (output columns n), the token rows
+// of the expert sit on the MMA N axis.  N of tcgen05.mma can be any multiple of 16 up to 256, so a tile of an expert
+// with 3 tokens issues N=16 MMAs, one with 100 tokens N=112: the ragged dimension costs no padding to 128 and the
+// tail of an expert never needs a clipped tensor-map store.  Every tile streams a [128 x K] slab of the expert's
+// weights exactly once through a 6-stage TMA ring, which is what bounds the layer (weights dominate the bytes).
+//
+//   warp 0    producer: TMA loads (weights tile, token tile, two 512-byte scale atoms) per 128-wide K step
+//   warp 1    tensor memory allocation + MMA issue (one elected lane): scale atoms smem -> TMEM (tcgen05.cp),
+//             4 x tcgen05.mma (K=32 each) per K step, tcgen05.commit to free the stage / publish the accumulator
+//   warps 2-5 epilogue: tcgen05.ld accumulator (lane = output column, column = token) -> bf16/fp16 -> global,
+//             each warp store writes 64 contiguous bytes of one output row; double-buffered against the MMAs
+//
+// Work list: tiles (expert, token tile of <=128, weight tile of 128) found with a per-CTA prefix scan over the
+// problem sizes (device resident: no host round trip), distributed round-robin over a persistent grid of one CTA
+// per SM.  Within an expert the token tile index runs fastest so that CTAs working at the same time read the same
+// weight slab (L2 reuse for heavy experts).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tensormap.cuh"
+
+namespace es_b200 {
+namespace mm {
+
+constexpr int THREADS = 192;
+constexpr int TILE_N = 128;     // weight rows per tile  (tcgen05.mma M)
+constexpr int TILE_K = 128;     // bytes of K per pipeline stage (one 128-byte swizzle atom)
+constexpr int TOK_TILE = 128;   // token rows per tile   (tcgen05.mma N, runtime multiple of 16)
+constexpr int STAGES = 6;
+constexpr int W_BYTES = TILE_N * TILE_K;
+constexpr int X_BYTES = TOK_TILE * TILE_K;
+constexpr int SF_BYTES = 512;
+constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // 33792, a multiple of 1024
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t ACC_COLS = 128;      // two accumulators: columns [0,128) and [128,256)
+constexpr uint32_t SFW_COL = 256;       // 4 columns: scales of the weight tile
+constexpr uint32_t SFX_COL = 260;       // 4 columns: scales of the token tile
+
+constexpr uint32_t ERR_PRODUCER = 1u, ERR_MMA = 2u, ERR_EPILOGUE = 4u;
+
+struct SharedCtl {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int warp_sums[32];
+  int tile_prefix[ES_B200_MAX_EXPERTS + 1];
+};
+
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(SharedCtl);
+
+__device__ uint32_t g_status = 0;   // sticky error bits of the grouped GEMM kernels (bounded waits that gave up)
+
+struct TileInfo {
+  int e, tt, nt;
+  int valid;     // token rows of this tile that belong to the expert
+  int n_mma;     // valid rounded up to 16
+  int row0;      // first token row in a / d
+};
+
+__device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
+                                                const int* expert_offsets) {
+  TileInfo ti;
+  ti.e = upper_bound_expert(prefix, num_experts, t);
+  const int i = t - prefix[ti.e];
+  const int m = problem_sizes[ti.e * 3];
+  const int token_tiles = (m + TOK_TILE - 1) / TOK_TILE;
+  ti.nt = i / token_tiles;
+  ti.tt = i - ti.nt * token_tiles;
+  const int rem = m - ti.tt * TOK_TILE;
+  ti.valid = rem < TOK_TILE ? rem : TOK_TILE;
+  ti.n_mma = (ti.valid + 15) & ~15;
+  ti.row0 = expert_offsets[ti.e] + ti.tt * TOK_TILE;
+  return ti;
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT from_f32(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+template <typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
+                        const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
+                        const __grid_constant__ CUtensorMap map_x128, const uint8_t* __restrict__ sf_tokens,
+                        const uint8_t* __restrict__ sf_weights, OutT* __restrict__ d,
+                        const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
+                        const int* __restrict__ blockscale_offsets, int num_experts, int n, int k) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + (size_t)STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&ctl->full[s], 1);
+      ptx::mbar_init(&ctl->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&ctl->tmem_full[a], 1);
+      ptx::mbar_init(&ctl->tmem_empty[a], 4);   // one arrival per epilogue warp
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&map_w);
+    ptx::prefetch_tensormap(&map_x16);
+    ptx::prefetch_tensormap(&map_x32);
+    ptx::prefetch_tensormap(&map_x64);
+    ptx::prefetch_tensormap(&map_x128);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  // everything above is independent of the previous kernel's output; problem sizes may not be
+  pdl_wait_prior_grid();
+  const int n_tiles = n / TILE_N;
+  block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
+    const int m = problem_sizes[e * 3];
+    return m > 0 ? ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles : 0;
+  });
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  pdl_launch_dependents();
+
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int total_tiles = ctl->tile_prefix[num_experts];
+  const int kt_count = k / TILE_K;
+  const int64_t sf_row_bytes = k / 32;
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_x128;
+        const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : 128u;
+        const uint32_t tx = W_BYTES + box_rows * TILE_K + 2 * SF_BYTES;
+        const uint8_t* sfw = sf_weights + (int64_t)ti.e * n * sf_row_bytes + (int64_t)ti.nt * kt_count * SF_BYTES;
+        const uint8_t* sfx = sf_tokens + (int64_t)blockscale_offsets[ti.e] * sf_row_bytes + (int64_t)ti.tt * kt_count * SF_BYTES;
+        const int w_row = ti.e * n + ti.nt * TILE_N;
+        for (int kt = 0; kt < kt_count; ++kt) {
+          if (!ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag)) {
+            ok = false;
+            *abort_flag = 1;
+            atomicOr(&g_status, ERR_PRODUCER);
+            break;
+          }
+          uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+          ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
+          ptx::tma_load_2d(stage, &map_w, &ctl->full[s], kt * TILE_K, w_row);
+          ptx::tma_load_2d(stage + W_BYTES, xm, &ctl->full[s], kt * TILE_K, ti.row0);
+          ptx::bulk_load(stage + W_BYTES + X_BYTES, sfw + (int64_t)kt * SF_BYTES, SF_BYTES, &ctl->full[s]);
+          ptx::bulk_load(stage + W_BYTES + X_BYTES + SF_BYTES, sfx + (int64_t)kt * SF_BYTES, SF_BYTES, &ctl->full[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      const uint32_t sfw_t = tmem_base + SFW_COL;
+      const uint32_t sfx_t = tmem_base + SFX_COL;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) { ok = false; }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        for (int kt = 0; ok && kt < kt_count; ++kt) {
+          if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
+          ptx::tc_cp_sf(sfw_t, ptx::make_desc_sf(stage + W_BYTES + X_BYTES));
+          ptx::tc_cp_sf(sfx_t, ptx::make_desc_sf(stage + W_BYTES + X_BYTES + SF_BYTES));
+          const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
+          const uint64_t b_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
+#pragma unroll
+          for (uint32_t j = 0; j < 4; ++j) {
+            ptx::tc_mma_mxf8(d_tmem, a_desc + 2 * j, b_desc + 2 * j, ptx::make_idesc_mxf8(TILE_N, ti.n_mma, j, j),
+                             sfw_t | (j << 30), sfx_t | (j << 30), (kt | j) != 0 ? 1u : 0u);
+          }
+          ptx::tc_commit(&ctl->empty[s]);      // stage reusable once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_MMA);
+          break;
+        }
+        ptx::tc_commit(&ctl->tmem_full[acc]);  // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;   // TMEM lane quadrant this warp may access
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_EPILOGUE);
+        }
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      OutT* dcol = d + (int64_t)ti.row0 * n + (ti.nt * TILE_N + q * 32 + lane);
+      for (int c0 = 0; c0 < ti.n_mma; c0 += 16) {
+        uint32_t v[16];
+        ptx::tc_ld_32x32b_x16(taddr + c0, v);
+        ptx::tc_wait_ld();
+        if (c0 + 16 >= ti.n_mma) {
+          // all of this warp's accumulator reads are done: hand the buffer back to the MMA warp
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int tok = c0 + j;
+          if (tok < ti.valid) dcol[(int64_t)tok * n] = from_f32<OutT>(__uint_as_float(v[j]));
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1u;
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <typename OutT>
+int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
+           const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, cudaStream_t stream) {
+  DeviceInfo info;
+  int rc = get_device_info(&info);
+  if (rc != ES_B200_OK) return rc;
+
+  CUtensorMap map_w, map_x[4];
+  rc = make_tensormap_u8_sw128(&map_w, b, (uint64_t)num_experts * n, (uint64_t)k, TILE_N);
+  if (rc != ES_B200_OK) return rc;
+  const uint32_t boxes[4] = {16, 32, 64, 128};
+  for (int i = 0; i < 4; ++i) {
+    rc = make_tensormap_u8_sw128(&map_x[i], a, (uint64_t)num_rows, (uint64_t)k, boxes[i]);
+    if (rc != ES_B200_OK) return rc;
+  }
+
+  auto kernel = mxfp8_grouped_mm_kernel<OutT>;
+  static bool configured[64] = {false};   // per device (one static per instantiation)
+  int dev = 0;
+  ES_CUDA_TRY(cudaGetDevice(&dev));
+  if (!configured[dev & 63]) {
+    ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    configured[dev & 63] = true;
+  }
+  // upper bound of the tile count known on the host: full token tiles of num_rows plus one partial per expert
+  const int64_t max_tiles = ((num_rows + TOK_TILE - 1) / TOK_TILE + num_experts) * (int64_t)(n / TILE_N);
+  const int grid = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sfa, sfb,
+                                 static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k));
+  return ES_B200_OK;
+}
+
+}  // namespace mm
+}  // namespace es_b200
+
+extern "C" size_t es_b200_grouped_mm_scratch_bytes(int, int64_t, int, int) { return 0; }
+
+extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d,
+                                        int out_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
+                                        const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n,
+                                        int k, int64_t sfa_rows, void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace es_b200;
+  (void)scratch; (void)scratch_bytes; (void)sfa_rows;
+  ES_REQUIRE(out_dtype == ES_B200_BF16 || out_dtype == ES_B200_FP16, "dtype must be kFloat16 or kBFloat16");
+  ES_REQUIRE(k > 0 && k % 128 == 0, "k should align 128");
+  ES_REQUIRE(n > 0 && n % 128 == 0, "n should align 128");
+  ES_REQUIRE(num_experts >= 0 && num_experts <= ES_B200_MAX_EXPERTS, "Number of experts cannot exceed %d",
+             ES_B200_MAX_EXPERTS);
+  ES_REQUIRE(num_rows >= 0 && num_rows < (int64_t)1 << 31, "num_rows out of range");
+  ES_REQUIRE((int64_t)num_experts * n < (int64_t)1 << 31, "num_experts * n out of range");
+  if (num_experts == 0 || num_rows == 0) return ES_B200_OK;
+  ES_REQUIRE(a && b && sfa && sfb && d && problem_sizes && expert_offsets && blockscale_offsets, "null pointer argument");
+  ES_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sfa) && aligned16(sfb), "a, b, sfa, sfb must be 16-byte aligned");
+  ES_REQUIRE((reinterpret_cast<uintptr_t>(d) & 1u) == 0, "d must be 2-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == ES_B200_BF16)
+    return mm::launch<__nv_bfloat16>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
+                                     num_rows, n, k, s);
+  return mm::launch<__half>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows,
+                            n, k, s);
+}
+
+extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {
+  using namespace es_b200;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint32_t v = 0;
+  ES_CUDA_TRY(cudaStreamSynchronize(s));
+  ES_CUDA_TRY(cudaMemcpyFromSymbol(&v, mm::g_status, sizeof(v)));
+  if (v != 0) {
+    uint32_t zero = 0;
+    ES_CUDA_TRY(cudaMemcpyToSymbol(mm::g_status, &zero, sizeof(zero)));
+  }
+  if (raw_status) *raw_status = v;
+  if (v != 0) return fail(ES_B200_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (status bits 0x%x)", v);
+  return ES_B200_OK;
+}

@@ -39,8 +39,8 @@ def _require_cuda(*tensors):
 
 
 def _scratch(lib, num_experts: int, num_rows: int, n: int, k: int, device) -> torch.Tensor:
-    nbytes = lib.es_b200_grouped_mm_scratch_bytes(num_experts, num_rows, n, k)
-    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+    nbytes = int(lib.es_b200_grouped_mm_scratch_bytes(num_experts, num_rows, n, k))
+    return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
 
 
 def es_sm100_mxfp8_blockscaled_grouped_quant(
@@ -115,7 +115,8 @@ def es_sm100_mxfp8_blockscaled_grouped_mm(
     _cabi.check(lib.es_b200_mxfp8_grouped_mm(
         a.data_ptr(), b.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), output.data_ptr(), dt,
         problem_sizes.data_ptr(), expert_offsets.data_ptr(), blockscale_offsets.data_ptr(), E, T, N, K, sfa_rows,
-        scratch.data_ptr(), scratch.numel(), _stream_ptr(a)))
+        scratch.data_ptr() if scratch is not None else None, scratch.numel() if scratch is not None else 0,
+        _stream_ptr(a)))
 
 
 def es_fp8_blockwise_scaled_grouped_mm(

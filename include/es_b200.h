@@ -66,8 +66,9 @@ int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, const int32_
 
 /*
  * Scratch requirement (bytes, device memory, 256-byte aligned) of the two grouped GEMM entry points for a call
- * with these extents.  Replaces the per-call torch::empty scratch tensors and the CUTLASS workspace of the
- * reference (es_sm100_mxfp8_blockscaled_launcher.cuh:163-176,140-142).  The contents need no initialisation.
+ * with these extents.  Stands where the reference allocates per-call torch::empty scratch tensors and a CUTLASS
+ * workspace (es_sm100_mxfp8_blockscaled_launcher.cuh:163-176,140-142).  The kernels build their work lists in
+ * shared memory, so this currently returns 0 and `scratch` may be NULL; callers should still ask.
  */
 size_t es_b200_grouped_mm_scratch_bytes(int num_experts, int64_t num_rows, int n, int k);
 
@@ -107,11 +108,12 @@ int es_b200_fp8_blockwise_grouped_mm(const void* a, const void* b, const float* 
 
 /*
  * Device-side status word of the grouped GEMMs.  Every wait inside the kernels is bounded; a wait that gives up
- * records a non-zero code in the first 4 bytes of `scratch` and the kernel exits cleanly.  This call copies that
- * word to the host (synchronising `stream`) and returns ES_B200_OK or ES_B200_ERR_DEVICE_TIMEOUT.  Optional:
- * intended for tests and debugging, never needed on the hot path.
+ * sets a bit in a library-owned device word and the kernel exits cleanly.  This call synchronises `stream`, copies
+ * that word to the host, clears it, and returns ES_B200_OK or ES_B200_ERR_DEVICE_TIMEOUT.  Optional: intended for
+ * tests and debugging, never needed on the hot path.  (No counterpart in the reference, which has no device-side
+ * error reporting.)
  */
-int es_b200_check_status(const void* scratch, void* stream, uint32_t* raw_status);
+int es_b200_check_status(void* stream, uint32_t* raw_status);
 
 #ifdef __cplusplus
 }

@@ -54,3 +54,51 @@ def valid_sf_index(counts, bo, K):
     idx = [int(bo[e]) * (K // 32) + Q.sf_swizzled_offsets(int(counts[e]), K).ravel()
            for e in range(len(counts)) if counts[e] > 0]
     return np.concatenate(idx) if idx else np.zeros(0, dtype=np.int64)
+
+
+# ---- grouped GEMM cases ------------------------------------------------------------------------
+def mxfp8_gemm_inputs(counts, N, K, seed, w_std=0.02):
+    """Seeded MXFP8 operands built on the CPU with the oracle quantiser (bit-identical to the CUDA quantiser):
+    returns dict of numpy arrays: a_codes [T,K], sfa flat, w_codes [E,N,K], sfb flat, ps, eo, bo."""
+    rng = np.random.default_rng(seed)
+    E = len(counts)
+    T = int(sum(counts))
+    ps, eo, bo, sfa_rows = Q.offsets_from_counts(counts, N, K)
+    a_bits = f32_to_bf16_bits(rng.standard_normal((max(T, 1), K), dtype=np.float32))[:T]
+    w_bits = f32_to_bf16_bits(rng.standard_normal((E * N, K), dtype=np.float32) * np.float32(w_std))
+    a_codes = np.zeros((T, K), dtype=np.uint8)
+    sfa = np.zeros(max(sfa_rows, 1) * (K // 32), dtype=np.uint8)
+    Q.grouped_quant(a_bits, True, ps, eo, bo, a_codes, sfa)
+    wps, weo, wbo, sfb_rows = Q.offsets_from_counts([N] * E, 0, K)
+    w_codes = np.zeros((E * N, K), dtype=np.uint8)
+    sfb = np.zeros(sfb_rows * (K // 32), dtype=np.uint8)
+    Q.grouped_quant(w_bits, True, wps, weo, wbo, w_codes, sfb)
+    return dict(a_codes=a_codes, sfa=sfa, w_codes=w_codes.reshape(E, N, K), sfb=sfb, ps=ps, eo=eo, bo=bo)
+
+
+def run_mxfp8_mm_op(inp, out_dtype=torch.bfloat16, device="cuda", fill=None):
+    """Calls the product GEMM through ops.py -> C ABI.  Returns d [T,N] on the CPU."""
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_mm
+    E, N, K = inp["w_codes"].shape
+    T = inp["a_codes"].shape[0]
+    a = torch.from_numpy(inp["a_codes"]).to(device).view(torch.float8_e4m3fn)
+    b = torch.from_numpy(inp["w_codes"]).to(device).view(torch.float8_e4m3fn).transpose(1, 2)   # [E,K,N] view
+    sfa = torch.from_numpy(inp["sfa"]).to(device)
+    sfb = torch.from_numpy(inp["sfb"]).to(device)
+    d = torch.zeros((T, N), dtype=out_dtype, device=device)
+    if fill is not None:
+        d.fill_(fill)
+    es_sm100_mxfp8_blockscaled_grouped_mm(
+        d, a, b, sfa, sfb, torch.from_numpy(inp["ps"]).to(device), torch.from_numpy(inp["eo"]).to(device),
+        torch.from_numpy(inp["bo"]).to(device))
+    torch.cuda.synchronize()
+    return d.cpu()
+
+
+def device_status():
+    from expert_specialization_moe_b200 import _cabi
+    import ctypes
+    lib = _cabi.load()
+    raw = ctypes.c_uint32(0)
+    rc = lib.es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
+    return rc, raw.value
