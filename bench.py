@@ -1,0 +1,390 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE grouped-GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gate_up|down|quant]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Default workload ("gate_up"): DeepSeek-V3-shaped gate_up MXFP8 grouped GEMM, prefill — E=256 experts, 32768 routed rows
+split by Zipf(1.2) counts, N=4096, K=7168, e4m3 operands with UE8M0 scales per 32, bf16 output.  One step = one call of
+es_sm100_mxfp8_blockscaled_grouped_mm over the whole batch.  With N GPUs the experts are sharded contiguously
+(E/N per GPU, expert-parallel, no data-path collective); the step time is the slowest rank's.
+
+Prints ONE JSON line (rank 0).  `value` is the device-timed throughput with operands resident in HBM; `e2e` is the same
+metric through the public op with the activations, their scales and the problem list copied from pinned host memory and
+the output copied back inside the timed region (weights are model state and stay resident).
+`--impl reference` times the CPU dequant+matmul path (the reference's torch path restated in oracle/) on a bounded
+sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (E, T, N, K, description)
+    "gate_up": (256, 32768, 4096, 7168, "DeepSeek-V3 gate_up MXFP8 grouped GEMM, prefill: E=256, 32768 routed rows "
+                                        "(4096 tokens x top-8), Zipf(1.2) counts, N=4096, K=7168"),
+    "down": (256, 512, 7168, 2048, "DeepSeek-V3 down-proj MXFP8 grouped GEMM, decode: E=256, 512 routed rows "
+                                   "(64 tokens x top-8), Zipf(1.2) counts, N=7168, K=2048"),
+}
+FALLBACK_HBM_GBS = 6650.0
+
+
+def zipf_counts(T, E, alpha=1.2, seed=0):
+    rng = np.random.default_rng(seed)
+    p = np.arange(1, E + 1, dtype=np.float64) ** -alpha
+    p /= p.sum()
+    counts = rng.multinomial(T, p)
+    rng.shuffle(counts)
+    return counts.astype(np.int64)
+
+
+def align128(x):
+    return (x + 127) // 128 * 128
+
+
+def offsets(counts, N, K):
+    counts = np.asarray(counts, dtype=np.int64)
+    E = len(counts)
+    eo = np.zeros(E, dtype=np.int32)
+    bo = np.zeros(E, dtype=np.int32)
+    eo[1:] = np.cumsum(counts)[:-1]
+    bo[1:] = np.cumsum(align128(counts))[:-1]
+    ps = np.stack([counts, np.full(E, N), np.full(E, K)], axis=1).astype(np.int32)
+    return ps, eo, bo, int(align128(counts).sum())
+
+
+def algorithmic_bytes(counts, N, K):
+    """A + SFA + B + SFB of the experts that have rows + bf16 D (padding rows and empty experts not counted)."""
+    counts = np.asarray(counts, dtype=np.int64)
+    T = int(counts.sum())
+    active = int((counts > 0).sum())
+    return T * K + T * K // 32 + active * N * K + active * N * K // 32 + 2 * T * N
+
+
+def peak_hbm():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def build_device_workload(counts, N, K, device, seed):
+    """Quantised operands resident on `device`, produced with this library's own grouped quant op (bit-identical to
+    the reference's): activations N(0,1), weights N(0,0.02), both bf16 -> e4m3 + UE8M0."""
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
+    E = len(counts)
+    T = int(counts.sum())
+    ps, eo, bo, sfa_rows = offsets(counts, N, K)
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    t = lambda a: torch.from_numpy(a).to(device)
+    ps_d, eo_d, bo_d = t(ps), t(eo), t(bo)
+    x = torch.randn((max(T, 1), K), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)[:T]
+    a = torch.zeros((T, K), dtype=torch.uint8, device=device).view(torch.float8_e4m3fn)
+    sfa = torch.zeros((max(sfa_rows, 1), K // 32), dtype=torch.uint8, device=device)
+    quant(x, ps_d, eo_d, bo_d, a, sfa)
+    del x
+    w = torch.empty((E, N, K), dtype=torch.uint8, device=device).view(torch.float8_e4m3fn)
+    sfb = torch.empty((E, N, K // 32), dtype=torch.uint8, device=device)
+    chunk = 8
+    for e0 in range(0, E, chunk):
+        ne = min(chunk, E - e0)
+        wb = (torch.randn((ne * N, K), generator=g, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+        wps, weo, wbo, _ = offsets([N] * ne, 0, K)
+        quant(wb, t(wps), t(weo), t(wbo), w[e0:e0 + ne].view(ne * N, K), sfb[e0:e0 + ne].view(ne * N, K // 32))
+        del wb
+    torch.cuda.synchronize(device)
+    d = torch.empty((T, N), dtype=torch.bfloat16, device=device)
+    return dict(a=a, sfa=sfa, b=w.transpose(1, 2), w=w, sfb=sfb, d=d, ps=ps_d, eo=eo_d, bo=bo_d,
+                ps_h=ps, eo_h=eo, bo_h=bo)
+
+
+def cpu_reference_rate(counts, N, K, seed, budget_s=20.0, threads=None):
+    """Times the CPU path (dequantise + per-expert fp32 torch.mm, oracle/grouped_gemm_oracle.py — the restatement of
+    the reference's torch dequant-matmul path) on a bounded sample: experts are taken in index order until the time
+    budget is used.  Returns (TFLOP/s, cores, description)."""
+    from oracle import grouped_gemm_oracle as G
+    from oracle import mxfp8_quant_oracle as Q
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    rng = np.random.default_rng(seed)
+    flops, secs, used = 0.0, 0.0, []
+
+    def random_mxfp8(rows):
+        # operand bytes drawn directly (finite e4m3 codes of either sign, scale exponents around 2^-7): the CPU time
+        # of dequantise + matmul does not depend on the values, and quantising 29 M weights per expert with the numpy
+        # oracle would dominate the wall clock of this leg
+        codes = rng.integers(0, 0x7F, size=(rows, K), dtype=np.uint8) | (rng.integers(0, 2, size=(rows, K), dtype=np.uint8) << 7)
+        sf = rng.integers(118, 123, size=(rows, K // 32), dtype=np.uint8)
+        return codes, torch.from_numpy(Q.swizzle_sf(sf, K))
+
+    wc, sfb = random_mxfp8(N)
+    w_t = torch.from_numpy(wc).view(1, N, K)
+    for e in range(len(counts)):
+        m = int(counts[e])
+        if m == 0:
+            continue
+        ac, sfa = random_mxfp8(m)
+        ps = np.array([[m, N, K]], dtype=np.int32)
+        a_t = torch.from_numpy(ac)
+        t0 = time.perf_counter()
+        G.mxfp8_grouped_mm(a_t, w_t, sfa, sfb, ps, [0], [0])
+        dt = time.perf_counter() - t0
+        secs += dt
+        flops += 2.0 * m * N * K
+        used.append(e)
+        if secs >= budget_s:
+            break
+    rate = flops / secs / 1e12 if secs > 0 else 0.0
+    rows = int(sum(int(counts[e]) for e in used))
+    desc = (f"experts {used[0]}..{used[-1]} of the workload ({len(used)} non-empty experts, {rows} rows, "
+            f"{flops / 1e9:.1f} GFLOP) in {secs:.1f} s: unswizzle + dequantise + fp32 torch.mm per expert")
+    return rate, threads, desc
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-budget", type=float, default=20.0, help="seconds of CPU work for the cpu_baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    E, T, N, K, desc = WORKLOADS[args.workload]
+    counts_all = zipf_counts(T, E, 1.2, 0)
+    metric = "MoE-layer grouped-GEMM TFLOPS"
+    config = {"workload": desc, "experts_per_gpu": E // max(world, 1), "placement": "contiguous",
+              "l2": "inputs larger than L2 (weights %.2f GB per GPU), no flush" % ((E // max(world, 1)) * N * K / 1e9),
+              "out_dtype": "bf16"}
+
+    if args.impl == "reference":
+        # the reference's CPU path, bounded sample per step; rank 0 only
+        if rank != 0:
+            return
+        rates = []
+        cores = os.cpu_count() or 1
+        per_step_budget = max(2.0, min(args.cpu_budget, 120.0 / max(1, args.steps + args.warmup)))
+        for i in range(args.warmup + args.steps):
+            r, cores, sdesc = cpu_reference_rate(counts_all, N, K, seed=100 + i, budget_s=per_step_budget)
+            if i >= args.warmup:
+                rates.append(r)
+        v = float(np.mean(rates)) if rates else 0.0
+        flops_total = 2.0 * T * N * K
+        line = {
+            "impl": "reference", "metric": metric, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": flops_total / (v * 1e12) * 1e3 if v else None,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp8_e4m3",
+            "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sdesc},
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --impl ours needs a CUDA device: the library has no CPU fallback")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+
+    # expert-parallel shard: contiguous E/world experts per rank
+    assert E % world == 0
+    e_lo, e_hi = rank * (E // world), (rank + 1) * (E // world)
+    counts = counts_all[e_lo:e_hi]
+    wl = build_device_workload(counts, N, K, device, seed=1000 + rank)
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_mm as grouped_mm
+    from expert_specialization_moe_b200 import _cabi
+
+    def step():
+        grouped_mm(wl["d"], wl["a"], wl["b"], wl["sfa"], wl["sfb"], wl["ps"], wl["eo"], wl["bo"])
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    lib = _cabi.load()
+    import ctypes
+    raw = ctypes.c_uint32(0)
+    rc = lib.es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
+    if rc != 0:
+        raise SystemExit(f"device-side status {raw.value:#x}: a bounded wait gave up; the timing is invalid")
+
+    # ---- end to end through the public op with host buffers
+    e2e = None
+    if not args.no_e2e:
+        a_h = wl["a"].view(torch.uint8).cpu().pin_memory()
+        sfa_h = wl["sfa"].cpu().pin_memory()
+        ps_h = torch.from_numpy(wl["ps_h"]).pin_memory()
+        eo_h = torch.from_numpy(wl["eo_h"]).pin_memory()
+        bo_h = torch.from_numpy(wl["bo_h"]).pin_memory()
+        d_h = torch.empty(wl["d"].shape, dtype=wl["d"].dtype).pin_memory()
+        a_d = torch.empty_like(wl["a"]); sfa_d = torch.empty_like(wl["sfa"])
+        ps_d = torch.empty_like(wl["ps"]); eo_d = torch.empty_like(wl["eo"]); bo_d = torch.empty_like(wl["bo"])
+
+        def e2e_step():
+            a_d.view(torch.uint8).copy_(a_h, non_blocking=True)
+            sfa_d.copy_(sfa_h, non_blocking=True)
+            ps_d.copy_(ps_h, non_blocking=True); eo_d.copy_(eo_h, non_blocking=True); bo_d.copy_(bo_h, non_blocking=True)
+            grouped_mm(wl["d"], a_d, wl["b"], sfa_d, wl["sfb"], ps_d, eo_d, bo_d)
+            d_h.copy_(wl["d"], non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        f1.record()
+        barrier()
+        e2e_ms = f0.elapsed_time(f1)
+        h2d = a_h.numel() + sfa_h.numel() + 4 * (ps_h.numel() + eo_h.numel() + bo_h.numel())
+        d2h = d_h.numel() * d_h.element_size()
+        e2e = (e2e_ms, h2d, d2h)
+
+    # ---- reduce over ranks: slowest rank's time, summed work
+    flops_local = 2.0 * float(counts.sum()) * N * K
+    stats = torch.tensor([elapsed_ms, e2e[0] if e2e else 0.0], dtype=torch.float64, device=device)
+    sums = torch.tensor([flops_local, float(e2e[1]) if e2e else 0.0, float(e2e[2]) if e2e else 0.0],
+                        dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    elapsed_ms, e2e_ms = float(stats[0]), float(stats[1])
+    flops_total, h2d_total, d2h_total = float(sums[0]), float(sums[1]), float(sums[2])
+
+    if rank == 0:
+        ms_per_step = elapsed_ms / args.steps
+        value = flops_total / (ms_per_step * 1e-3) / 1e12
+        peak, peak_kind = peak_hbm()
+        # roofline of the dominant (only) kernel, rank 0's launch: algorithmic bytes of rank 0's shard / its own time
+        abytes = algorithmic_bytes(counts, N, K)
+        my_ms = float(ev0.elapsed_time(ev1)) / args.steps
+        achieved = abytes / (my_ms * 1e-3) / 1e9
+        traffic = None
+        tf = ROOT / "profiles" / "traffic.json"
+        if tf.exists():
+            try:
+                traffic = json.loads(tf.read_text()).get(f"{args.workload}_n{world}")
+            except Exception:
+                traffic = None
+        line = {
+            "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "mxfp8_e4m3", "data": "synthetic",
+            "config": config,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "peak_kind": peak_kind, "algorithmic_bytes": abytes,
+                         "kernel": "mxfp8_grouped_mm_kernel", "kernel_ms": my_ms},
+            "clocks": clocks, "gpu_launches": args.steps,
+        }
+        if e2e:
+            e2e_step_ms = e2e_ms / args.steps
+            line["e2e"] = {"value": flops_total / (e2e_step_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total),
+                           "ms_per_step": e2e_step_ms}
+        if world == 1 and not args.no_cpu_baseline:
+            r, cores, sdesc = cpu_reference_rate(counts_all, N, K, seed=100, budget_s=args.cpu_budget)
+            line["cpu_baseline"] = {"value": r, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sdesc}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
