@@ -38,6 +38,12 @@ WORKLOADS = {
                                         "(4096 tokens x top-8), Zipf(1.2) counts, N=4096, K=7168"),
     "down": (256, 512, 7168, 2048, "DeepSeek-V3 down-proj MXFP8 grouped GEMM, decode: E=256, 512 routed rows "
                                    "(64 tokens x top-8), Zipf(1.2) counts, N=7168, K=2048"),
+    # small cases for profiler captures (a few GB at most on the device; weights still larger than L2)
+    "gate_up_small": (32, 4096, 4096, 7168, "gate_up shape at 1/8 scale for profiler captures: E=32, 4096 routed rows, "
+                                            "Zipf(1.2) counts, N=4096, K=7168"),
+    "down_small": (64, 128, 7168, 2048, "down-proj shape at 1/4 scale for profiler captures: E=64, 128 routed rows, "
+                                        "Zipf(1.2) counts, N=7168, K=2048"),
+    "heavy": (8, 32768, 4096, 7168, "compute-bound probe: E=8 experts x 4096 rows each, N=4096, K=7168"),
 }
 FALLBACK_HBM_GBS = 6650.0
 
@@ -223,7 +229,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     E, T, N, K, desc = WORKLOADS[args.workload]
-    counts_all = zipf_counts(T, E, 1.2, 0)
+    counts_all = zipf_counts(T, E, 1.2, 0) if args.workload != "heavy" else np.full(E, T // E, dtype=np.int64)
     metric = "MoE-layer grouped-GEMM TFLOPS"
     config = {"workload": desc, "experts_per_gpu": E // max(world, 1), "placement": "contiguous",
               "l2": "inputs larger than L2 (weights %.2f GB per GPU), no flush" % ((E // max(world, 1)) * N * K / 1e9),

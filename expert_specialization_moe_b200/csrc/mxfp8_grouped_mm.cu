@@ -20,6 +20,7 @@
 // weight slab (L2 reuse for heavy experts).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -305,6 +306,14 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
 }
 
 }  // namespace mm
+
+namespace mm2 {   // CTA-pair kernel (mxfp8_grouped_mm_pair.cu)
+int launch_bf16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
+                const int32_t*, int, int64_t, int, int, int64_t, cudaStream_t);
+int launch_fp16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
+                const int32_t*, int, int64_t, int, int, int64_t, cudaStream_t);
+int read_and_clear_status(uint32_t* out);
+}  // namespace mm2
 }  // namespace es_b200
 
 extern "C" size_t es_b200_grouped_mm_scratch_bytes(int, int64_t, int, int) { return 0; }
@@ -314,7 +323,7 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
                                         const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n,
                                         int k, int64_t sfa_rows, void* scratch, size_t scratch_bytes, void* stream) {
   using namespace es_b200;
-  (void)scratch; (void)scratch_bytes; (void)sfa_rows;
+  (void)scratch; (void)scratch_bytes;
   ES_REQUIRE(out_dtype == ES_B200_BF16 || out_dtype == ES_B200_FP16, "dtype must be kFloat16 or kBFloat16");
   ES_REQUIRE(k > 0 && k % 128 == 0, "k should align 128");
   ES_REQUIRE(n > 0 && n % 128 == 0, "n should align 128");
@@ -327,6 +336,23 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
   ES_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sfa) && aligned16(sfb), "a, b, sfa, sfb must be 16-byte aligned");
   ES_REQUIRE((reinterpret_cast<uintptr_t>(d) & 1u) == 0, "d must be 2-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Tile-shape specialisation by what the host knows without a device round trip (rows per expert on average):
+  // few rows per expert (decode) -> the layer streams weights, independent single CTAs with 128 x <=128 tiles keep
+  // the most bytes in flight; many rows per expert (prefill) -> CTA pairs with 256 x <=192 tiles halve the operand
+  // bytes per FLOP that each SM pulls through L2.  ES_B200_MM_KERNEL=single|pair overrides (for A/B measurements).
+  static const int forced = [] {
+    const char* v = getenv("ES_B200_MM_KERNEL");
+    return !v ? 0 : v[0] == 's' ? 1 : v[0] == 'p' ? 2 : 0;
+  }();
+  const bool use_pair = forced == 2 || (forced == 0 && num_rows >= (int64_t)32 * num_experts);
+  if (use_pair) {
+    ES_REQUIRE(sfa_rows >= 0, "sfa_rows must be non-negative");
+    if (out_dtype == ES_B200_BF16)
+      return mm2::launch_bf16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
+                              num_rows, n, k, sfa_rows, s);
+    return mm2::launch_fp16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
+                            num_rows, n, k, sfa_rows, s);
+  }
   if (out_dtype == ES_B200_BF16)
     return mm::launch<__nv_bfloat16>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
                                      num_rows, n, k, s);
@@ -344,6 +370,10 @@ extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {
     uint32_t zero = 0;
     ES_CUDA_TRY(cudaMemcpyToSymbol(mm::g_status, &zero, sizeof(zero)));
   }
+  uint32_t v2 = 0;
+  int rc2 = mm2::read_and_clear_status(&v2);
+  if (rc2 != ES_B200_OK) return rc2;
+  v |= v2;
   if (raw_status) *raw_status = v;
   if (v != 0) return fail(ES_B200_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (status bits 0x%x)", v);
   return ES_B200_OK;

@@ -44,4 +44,21 @@ inline int make_tensormap_u8_sw128(CUtensorMap* map, const void* base, uint64_t 
   return ES_B200_OK;
 }
 
+// Array of 512-byte records (the swizzled scale-factor atoms) viewed as [count, 128] uint32; box = one record,
+// no swizzle: a load places the 512 bytes contiguously in shared memory.
+inline int make_tensormap_records512(CUtensorMap* map, const void* base, uint64_t count) {
+  EncodeTiledFn fn;
+  int rc = get_encode_fn(&fn);
+  if (rc != ES_B200_OK) return rc;
+  cuuint64_t dims[2] = {128, count};
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ES_B200_ERR_CUDA, "cuTensorMapEncodeTiled (records) failed with CUresult %d", (int)r);
+  return ES_B200_OK;
+}
+
 }  // namespace es_b200

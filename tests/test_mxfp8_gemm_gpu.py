@@ -42,6 +42,9 @@ def _check_against_oracle(inp, d, out_dtype):
     ([0, 1, 3, 7, 16, 64, 128, 293], 1024, 512),
     ([0, 0, 0], 128, 128),
     ([17, 33, 65, 129], 384, 1152),
+    ([193, 385, 577, 64], 256, 256),      # token tiles that start mid scale-atom
+    ([1000], 128, 128),                   # odd number of 128-wide weight tiles: one CTA of the pair idles
+    ([200, 9], 384, 256),
 ])
 def test_mm_matches_oracle(counts, N, K, out_dtype):
     inp = C.mxfp8_gemm_inputs(counts, N, K, seed=N + K + len(counts))
