@@ -314,6 +314,9 @@ int launch_fp16(const void*, const void*, const uint8_t*, const uint8_t*, void*,
                 const int32_t*, int, int64_t, int, int, int64_t, cudaStream_t);
 int read_and_clear_status(uint32_t* out);
 }  // namespace mm2
+namespace bw {    // FP8-blockwise kernel (fp8_blockwise_grouped_mm.cu)
+int read_and_clear_status(uint32_t* out);
+}
 }  // namespace es_b200
 
 extern "C" size_t es_b200_grouped_mm_scratch_bytes(int, int64_t, int, int) { return 0; }
@@ -372,6 +375,9 @@ extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {
   }
   uint32_t v2 = 0;
   int rc2 = mm2::read_and_clear_status(&v2);
+  if (rc2 != ES_B200_OK) return rc2;
+  v |= v2;
+  rc2 = bw::read_and_clear_status(&v2);
   if (rc2 != ES_B200_OK) return rc2;
   v |= v2;
   if (raw_status) *raw_status = v;

@@ -169,5 +169,6 @@ def es_fp8_blockwise_scaled_grouped_mm(
     scratch = _scratch(lib, E, T, N, K, a.device)
     _cabi.check(lib.es_b200_fp8_blockwise_grouped_mm(
         a.data_ptr(), b.data_ptr(), scales_a.data_ptr(), scales_b.data_ptr(), output.data_ptr(), dt,
-        problem_sizes.data_ptr(), expert_offsets.data_ptr(), E, T, N, K, scratch.data_ptr(), scratch.numel(),
+        problem_sizes.data_ptr(), expert_offsets.data_ptr(), E, T, N, K,
+        scratch.data_ptr() if scratch is not None else None, scratch.numel() if scratch is not None else 0,
         _stream_ptr(a)))

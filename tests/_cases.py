@@ -102,3 +102,43 @@ def device_status():
     raw = ctypes.c_uint32(0)
     rc = lib.es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
     return rc, raw.value
+
+
+def fp8_blockwise_inputs(counts, N, K, seed, dtype=torch.bfloat16):
+    """Operands of the FP8-blockwise op built with the (restated) reference quantisers on the CPU."""
+    from oracle import grouped_gemm_oracle as G
+    g = torch.Generator().manual_seed(seed)
+    E, T = len(counts), int(sum(counts))
+    ps, eo, _, _ = Q.offsets_from_counts(counts, N, K)
+    a = torch.randn((max(T, 1), K), generator=g, dtype=torch.float32).to(dtype)[:T]
+    w = torch.randn((E, N, K), generator=g, dtype=torch.float32).to(dtype)
+    if T:
+        a_q, sa = G.per_token_cast_to_fp8(a)
+    else:
+        a_q, sa = torch.zeros((0, K), dtype=torch.float8_e4m3fn), torch.zeros((0, K // 128))
+    w_q = torch.empty((E, N, K), dtype=torch.float8_e4m3fn)
+    sb = torch.empty((E, N // 128, K // 128), dtype=torch.float32)
+    for e in range(E):
+        w_q[e], sb[e] = G.per_block_cast_to_fp8(w[e])
+    return dict(a=a, w=w, a_q=a_q.contiguous(), sa=sa.float().contiguous(), w_q=w_q, sb=sb, ps=ps, eo=eo)
+
+
+def run_fp8_blockwise_op(inp, out_dtype=torch.bfloat16, device="cuda", fill=None):
+    from expert_specialization_moe_b200 import es_fp8_blockwise_scaled_grouped_mm
+    E, N, K = inp["w_q"].shape
+    T = inp["a_q"].shape[0]
+    a = inp["a_q"].to(device)
+    b = inp["w_q"].to(device).transpose(1, 2)                 # [E, K, N] view, stride(1) == 1
+    sa = inp["sa"].to(device)
+    sb = inp["sb"].to(device).transpose(1, 2)                 # [E, K/128, N/128] view
+    d = torch.zeros((T, N), dtype=out_dtype, device=device)
+    if fill is not None:
+        d.fill_(fill)
+    strides = torch.full((E,), K, dtype=torch.int64, device=device)
+    d_strides = torch.full((E,), N, dtype=torch.int64, device=device)
+    workspace = torch.empty(1024, dtype=torch.uint8, device=device)
+    es_fp8_blockwise_scaled_grouped_mm(d, a, b, sa, sb, strides, strides, d_strides,
+                                       torch.from_numpy(inp["ps"]).to(device), torch.from_numpy(inp["eo"]).to(device),
+                                       workspace)
+    torch.cuda.synchronize()
+    return d.cpu()

@@ -1,0 +1,66 @@
+"""GPU parity of the FP8-blockwise grouped GEMM (fp32 scales: 1x128 on A, 128x128 on B) against the restated torch
+dequant-matmul path of the reference's test (test/test_es_grouped_gemm.py:36-86).  Floating point: relative error
+<= 1e-2, cosine >= 0.9999 versus the dequantised fp32 matmul, and the reference test's own acceptance
+calc_diff < 1e-3 versus the UNQUANTISED matmul (test_es_grouped_gemm.py:140,195-199)."""
+import pytest
+import torch
+
+from oracle import grouped_gemm_oracle as G
+from tests import _cases as C
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(inp, d, out_dtype):
+    ref = G.fp8_blockwise_grouped_mm(inp["a_q"].view(torch.uint8), inp["w_q"].view(torch.uint8), inp["sa"], inp["sb"],
+                                     inp["ps"], inp["eo"], out_dtype=out_dtype)
+    for e in range(len(inp["ps"])):
+        m, off = int(inp["ps"][e][0]), int(inp["eo"][e])
+        if m == 0:
+            continue
+        rel, cos = G.rel_err_and_cosine(d[off:off + m].float(), ref[off:off + m].float())
+        assert rel <= 1e-2 and cos >= 0.9999, f"expert {e} (m={m}): rel={rel:.3e} cos={cos:.6f}"
+        unq = inp["a"][off:off + m].float() @ inp["w"][e].float().t()
+        assert G.calc_diff(d[off:off + m], unq) < 1e-3
+    rc, raw = C.device_status()
+    assert rc == 0, f"device status {raw:#x}"
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("counts,N,K", [
+    ([0, 1, 3, 7, 16, 64, 128, 293], 1024, 512),     # the CPU-runnable configuration of the build target
+    ([1], 128, 128),
+    ([130, 0, 77], 256, 384),
+    ([200, 31], 128, 7168),
+])
+def test_blockwise_matches_oracle(counts, N, K, out_dtype):
+    inp = C.fp8_blockwise_inputs(counts, N, K, seed=0, dtype=out_dtype)
+    d = C.run_fp8_blockwise_op(inp, out_dtype)
+    _check(inp, d, out_dtype)
+
+
+def test_blockwise_reference_test_shapes():
+    """The reference's own test draws n, k in 128*[1,64], m in [1,256], E in {8..128}; one seeded draw of that family."""
+    import random
+    rnd = random.Random(3)
+    E = 16
+    N, K = rnd.randint(1, 16) * 128, rnd.randint(1, 16) * 128
+    counts = [rnd.randint(1, 256) for _ in range(E)]
+    inp = C.fp8_blockwise_inputs(counts, N, K, seed=1)
+    d = C.run_fp8_blockwise_op(inp)
+    _check(inp, d, torch.bfloat16)
+
+
+def test_blockwise_rejects_bad_arguments():
+    inp = C.fp8_blockwise_inputs([4], 128, 128, seed=2)
+    from expert_specialization_moe_b200 import es_fp8_blockwise_scaled_grouped_mm as op
+    dev = "cuda"
+    a = inp["a_q"].to(dev); b = inp["w_q"].to(dev).transpose(1, 2)
+    sa = inp["sa"].to(dev); sb = inp["sb"].to(dev).transpose(1, 2)
+    ps = torch.from_numpy(inp["ps"]).to(dev); eo = torch.from_numpy(inp["eo"]).to(dev)
+    st = torch.full((1,), 128, dtype=torch.int64, device=dev)
+    ws = torch.empty(16, dtype=torch.uint8, device=dev)
+    with pytest.raises(RuntimeError, match="output must be bfloat16 or half"):
+        op(torch.zeros((4, 128), dtype=torch.float32, device=dev), a, b, sa, sb, st, st, st, ps, eo, ws)
+    with pytest.raises(RuntimeError, match="problem_sizes must be int32"):
+        op(torch.zeros((4, 128), dtype=torch.bfloat16, device=dev), a, b, sa, sb, st, st, st, ps.long(), eo, ws)
