@@ -1,0 +1,72 @@
+"""CPU tests of the drop-in boundary: the C-ABI library builds for sm_100a without a GPU, loads, exports every symbol
+that include/es_b200.h declares, and rejects bad arguments before touching the device.  No compute is launched."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from expert_specialization_moe_b200 import _cabi
+    return _cabi.load()
+
+
+def test_library_exports_every_declared_symbol(lib):
+    header = (ROOT / "include" / "es_b200.h").read_text()
+    names = sorted(set(re.findall(r"\b(es_b200_[a-z0-9_]+)\s*\(", header)))
+    assert len(names) >= 8
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/es_b200.h but not exported"
+
+
+def test_version_and_error_strings(lib):
+    assert b"sm_100a" in lib.es_b200_version()
+    assert lib.es_b200_strerror(0) == b"ok"
+    assert b"invalid" in lib.es_b200_strerror(1)
+
+
+def test_argument_checks_happen_before_any_launch(lib):
+    # k not a multiple of 128 / bad dtype / too many experts: rejected on the host (no CUDA call is needed for that)
+    rc = lib.es_b200_mxfp8_grouped_quant(None, 0, None, None, None, None, None, 4, 16, 100, None)
+    assert rc == 1 and b"k must align to 128" in lib.es_b200_last_error()
+    rc = lib.es_b200_mxfp8_grouped_quant(None, 7, None, None, None, None, None, 4, 16, 128, None)
+    assert rc == 1 and b"kFloat16 or kBFloat16" in lib.es_b200_last_error()
+    rc = lib.es_b200_mxfp8_grouped_mm(None, None, None, None, None, 0, None, None, None, 2000, 16, 128, 128, 0, None, 0,
+                                      None)
+    assert rc == 1 and b"Number of experts cannot exceed 1024" in lib.es_b200_last_error()
+    rc = lib.es_b200_fp8_blockwise_grouped_mm(None, None, None, None, None, 0, None, None, 4, 16, 100, 128, None, 0, None)
+    assert rc == 1 and b"n should align 128" in lib.es_b200_last_error()
+    assert lib.es_b200_grouped_mm_scratch_bytes(8, 512, 1024, 512) == 0
+
+
+def test_ops_mirror_reference_signatures():
+    import inspect
+    from expert_specialization_moe_b200 import ops
+    sig = lambda f: list(inspect.signature(f).parameters)
+    assert sig(ops.es_sm100_mxfp8_blockscaled_grouped_quant) == [
+        "input", "problem_sizes", "expert_offsets", "blockscale_offsets", "quant_output", "scale_factor"]
+    assert sig(ops.es_sm100_mxfp8_blockscaled_grouped_mm) == [
+        "output", "a", "b", "sfa", "sfb", "problem_sizes", "expert_offsets", "blockscale_offsets"]
+    assert sig(ops.es_fp8_blockwise_scaled_grouped_mm) == [
+        "output", "a", "b", "scales_a", "scales_b", "stride_a", "stride_b", "stride_d", "problem_sizes",
+        "expert_offsets", "workspace"]
+
+
+def test_ops_have_no_cpu_fallback():
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
+    x = torch.zeros((4, 128), dtype=torch.bfloat16)
+    ps = torch.tensor([[4, 0, 128]], dtype=torch.int32)
+    z = torch.zeros(1, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="CUDA-only"):
+        quant(x, ps, z, z, torch.zeros((4, 128), dtype=torch.uint8), torch.zeros((128, 4), dtype=torch.uint8))
+
+
+def test_product_does_not_import_the_oracle():
+    for f in (ROOT / "expert_specialization_moe_b200").rglob("*.py"):
+        txt = f.read_text()
+        assert "import oracle" not in txt and "from oracle" not in txt, f
