@@ -44,6 +44,11 @@ WORKLOADS = {
     "down_small": (64, 128, 7168, 2048, "down-proj shape at 1/4 scale for profiler captures: E=64, 128 routed rows, "
                                         "Zipf(1.2) counts, N=7168, K=2048"),
     "heavy": (8, 32768, 4096, 7168, "compute-bound probe: E=8 experts x 4096 rows each, N=4096, K=7168"),
+    # grouped MXFP8 quantisation alone (N is unused): bf16 N(0,1) with 1% outliers x50
+    "quant": (256, 32768, 0, 7168, "grouped MXFP8 quantisation: bf16 [32768, 7168], E=256, Zipf(1.2) counts, "
+                                   "e4m3 codes + swizzled UE8M0 scales"),
+    "quant_small": (64, 8192, 0, 7168, "grouped MXFP8 quantisation at 1/4 scale for profiler captures: bf16 "
+                                       "[8192, 7168], E=64"),
 }
 FALLBACK_HBM_GBS = 6650.0
 
@@ -90,6 +95,18 @@ def peak_hbm():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def read_traffic(key):
+    """DRAM bytes per launch from the committed ncu capture summary (profiles/traffic.txt), or None."""
+    f = ROOT / "profiles" / "traffic.txt"
+    if not f.exists():
+        return None
+    for line in f.read_text().splitlines():
+        p = line.split()
+        if len(p) == 2 and p[0] == key:
+            return float(p[1])
+    return None
+
+
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -103,7 +120,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.idx), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
@@ -211,11 +228,70 @@ def cpu_reference_rate(counts, N, K, seed, budget_s=20.0, threads=None):
     return rate, threads, desc
 
 
+def bench_quant(args, E, T, K, desc, device, rank, world, dist):
+    """Grouped quant alone; with N GPUs each rank quantises its own E/N experts' rows (no collective)."""
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
+    counts_all = zipf_counts(T, E, 1.2, 0)
+    counts = counts_all[rank * (E // world):(rank + 1) * (E // world)]
+    Tl = int(counts.sum())
+    ps, eo, bo, sf_rows = offsets(counts, 0, K)
+    t = lambda a: torch.from_numpy(a).to(device)
+    ps, eo, bo = t(ps), t(eo), t(bo)
+    g = torch.Generator(device=device); g.manual_seed(7 + rank)
+    x = torch.randn((Tl, K), generator=g, device=device, dtype=torch.float32)
+    x = (x * torch.where(torch.rand((Tl, K), generator=g, device=device) < 0.01, 50.0, 1.0)).to(torch.bfloat16)
+    codes = torch.empty((Tl, K), dtype=torch.uint8, device=device).view(torch.float8_e4m3fn)
+    sf = torch.empty((max(sf_rows, 128), K // 32), dtype=torch.uint8, device=device)
+    step = lambda: quant(x, ps, eo, bo, codes, sf)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # the 0.7 GB working set is larger than L2, but consecutive steps re-read the same input: flush L2 between steps
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(device.index or 0)
+    if rank == 0:
+        sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for e0, e1 in evs:
+        flush.zero_()
+        e0.record(); step(); e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = sum(e0.elapsed_time(e1) for e0, e1 in evs) / args.steps
+    abytes_local = 3 * Tl * K + Tl * K // 32
+    stats = torch.tensor([ms], dtype=torch.float64, device=device)
+    sums = torch.tensor([float(abytes_local)], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        peak, peak_kind = peak_hbm()
+        achieved = abytes_local / (ms * 1e-3) / 1e9
+        line = {"metric": "MXFP8 grouped quantisation GB/s (algorithmic bytes)", "value": float(sums[0]) / (float(stats[0]) * 1e-3) / 1e9,
+                "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(stats[0]),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16->e4m3+ue8m0",
+                "data": "synthetic", "config": {"workload": desc, "l2": "256 MiB flush buffer written between steps"},
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "traffic": read_traffic(f"{args.workload}_n{world}"), "peak_kind": peak_kind, "algorithmic_bytes": abytes_local,
+                             "kernel": "mxfp8_group_quant_kernel", "kernel_ms": ms},
+                "clocks": clocks, "gpu_launches": args.steps}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
@@ -270,6 +346,9 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+
+    if args.workload.startswith("quant"):
+        return bench_quant(args, E, T, K, desc, device, rank, world, dist)
 
     # expert-parallel shard: contiguous E/world experts per rank
     assert E % world == 0
@@ -361,13 +440,7 @@ def main():
         abytes = algorithmic_bytes(counts, N, K)
         my_ms = float(ev0.elapsed_time(ev1)) / args.steps
         achieved = abytes / (my_ms * 1e-3) / 1e9
-        traffic = None
-        tf = ROOT / "profiles" / "traffic.json"
-        if tf.exists():
-            try:
-                traffic = json.loads(tf.read_text()).get(f"{args.workload}_n{world}")
-            except Exception:
-                traffic = None
+        traffic = read_traffic(f"{args.workload}_n{world}")
         line = {
             "metric": metric, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
@@ -375,7 +448,8 @@ def main():
             "config": config,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": peak_kind, "algorithmic_bytes": abytes,
-                         "kernel": "mxfp8_grouped_mm_kernel", "kernel_ms": my_ms},
+                         "kernel": ("mxfp8_grouped_mm_pair_kernel" if int(counts.sum()) >= 32 * len(counts)
+                                    else "mxfp8_grouped_mm_kernel"), "kernel_ms": my_ms},
             "clocks": clocks, "gpu_launches": args.steps,
         }
         if e2e:
