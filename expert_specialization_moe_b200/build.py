@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
-] + (["-DES_PROFILE"] if os.environ.get("ES_PROFILE") else [])
+] + (["-DES_PROFILE"] if os.environ.get("ES_PROFILE") else []) + os.environ.get("ES_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:

@@ -188,60 +188,71 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   volatile int* abort_flag = &ctl->abort_flag;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ producer (one lane in each CTA)
-    if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
+    // ------------------------------------------------------------------ producer (warp 0 of each CTA)
+    // The whole warp walks the work list; per K step lanes 0..4 each issue ONE of the stage's loads in the same
+    // instruction (a TMA issue costs the issuing thread ~80 cycles, five in a row would be a third of a stage time).
+    int s = 0;
+    uint32_t ph = 0;
+    const bool mixed = ctl->tile_prefix[1][num_experts] > 0;
+#ifdef ES_PROFILE
+    long long _acc[4] = {0, 0, 0, 0};
+#endif
+    PROF_T0();
+    for (int t = pair; t < total_tiles; t += num_pairs) {
+      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const int half = ti.n_mma >> 1;                       // token rows held by each CTA
+      const int xi = half <= 8 ? 0 : half <= 16 ? 1 : half <= 32 ? 2 : half <= 64 ? 3 : 4;
+      const uint32_t box_rows = xi == 0 ? 8u : xi == 1 ? 16u : xi == 2 ? 32u : xi == 3 ? 64u : 96u;
+      const uint32_t tx = 2u * (W_BYTES + box_rows * TILE_K + SFW_BYTES + (uint32_t)ti.n_atoms * 512u);
+      int nt = ti.np * 2 + (int)rank;
+      const int w_row = ti.e * n + nt * TILE_N;             // may run past the expert when n/128 is odd: not stored
+      if (nt >= n_tiles) nt = n_tiles - 1;                  // keep the scale-atom load inside the buffer
+      const int sfw_atom = ti.e * sfw_atoms_per_expert + nt * kt_count;
+      const int sfx_atom = ((blockscale_offsets[ti.e] >> 7) + ti.atom0) * kt_count;
+      const int x_row = ti.row0 + (int)rank * half;
+      // weights of single-tile experts are used once: do not let them push the re-read working set out of L2
+      const uint64_t w_hint = ti.heavy ? ptx::kL2EvictLast : (mixed ? ptx::kL2EvictFirst : ptx::kL2EvictNormal);
+      // this lane's load: 0 weights, 1 tokens, 2 weight scales, 3 / 4 token scale atoms
+      const int n_ops = 4 + (ti.n_atoms > 1 ? 1 : 0);
+      const CUtensorMap* my_map = lane == 0 ? &maps.w : lane == 1 ? &maps.x[xi] : lane == 2 ? &maps.sfw : &maps.sfx;
+      const uint32_t my_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)W_BYTES : lane == 2 ? (uint32_t)(W_BYTES + X_BYTES)
+                              : lane == 3 ? (uint32_t)(W_BYTES + X_BYTES + SFW_BYTES)
+                                          : (uint32_t)(W_BYTES + X_BYTES + SFW_BYTES + 512);
+      const int my_c1 = lane == 0 ? w_row : lane == 1 ? x_row : lane == 2 ? sfw_atom : lane == 3 ? sfx_atom
+                                                                                               : sfx_atom + kt_count;
+      const uint64_t my_hint = lane == 0 ? w_hint : lane == 1 ? ptx::kL2EvictLast : ptx::kL2EvictNormal;
       bool ok = true;
-      const bool mixed = ctl->tile_prefix[1][num_experts] > 0;
+      for (int kt = 0; kt < kt_count; ++kt) {
+        ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag));
+        if (!ok) break;
+        PROF_ADD(0);
 #ifdef ES_PROFILE
-      long long _acc[4] = {0, 0, 0, 0};
+        if (rank == 0 && lane == 0) { ctl->t_issue[s] = clock64(); if (ctl->t_commit[s]) _acc[2] += ctl->t_issue[s] - ctl->t_commit[s]; }
 #endif
-      PROF_T0();
-      for (int t = pair; ok && t < total_tiles; t += num_pairs) {
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-        const int half = ti.n_mma >> 1;                       // token rows held by each CTA
-        const int xi = half <= 8 ? 0 : half <= 16 ? 1 : half <= 32 ? 2 : half <= 64 ? 3 : 4;
-        const uint32_t box_rows = xi == 0 ? 8u : xi == 1 ? 16u : xi == 2 ? 32u : xi == 3 ? 64u : 96u;
-        const uint32_t tx = 2u * (W_BYTES + box_rows * TILE_K + SFW_BYTES + (uint32_t)ti.n_atoms * 512u);
-        int nt = ti.np * 2 + (int)rank;
-        const int w_row = ti.e * n + nt * TILE_N;             // may run past the expert when n/128 is odd: not stored
-        if (nt >= n_tiles) nt = n_tiles - 1;                  // keep the scale-atom load inside the buffer
-        const int sfw_atom = ti.e * sfw_atoms_per_expert + nt * kt_count;
-        const int sfx_atom = ((blockscale_offsets[ti.e] >> 7) + ti.atom0) * kt_count;
-        const int x_row = ti.row0 + (int)rank * half;
-        for (int kt = 0; kt < kt_count; ++kt) {
-          if (!ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag)) {
-            ok = false;
-            *abort_flag = 1;
-            atomicOr(&g_status, ERR_PRODUCER);
-            break;
-          }
-          PROF_ADD(0);
-#ifdef ES_PROFILE
-          if (rank == 0) { ctl->t_issue[s] = clock64(); if (ctl->t_commit[s]) _acc[2] += ctl->t_issue[s] - ctl->t_commit[s]; }
-#endif
-          uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
-          if (rank == 0) ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
-          // weights of single-tile experts are used once: do not let them push the re-read working set out of L2
-          const uint64_t w_hint = ti.heavy ? ptx::kL2EvictLast : (mixed ? ptx::kL2EvictFirst : ptx::kL2EvictNormal);
-          ptx::tma_load_2d_pair_hint(stage, &maps.w, &ctl->full[s], kt * TILE_K, w_row, w_hint);
-          ptx::tma_load_2d_pair_hint(stage + W_BYTES, &maps.x[xi], &ctl->full[s], kt * TILE_K, x_row, ptx::kL2EvictLast);
-          ptx::tma_load_2d_pair(stage + W_BYTES + X_BYTES, &maps.sfw, &ctl->full[s], 0, sfw_atom + kt);
-          ptx::tma_load_2d_pair(stage + W_BYTES + X_BYTES + SFW_BYTES, &maps.sfx, &ctl->full[s], 0, sfx_atom + kt);
-          if (ti.n_atoms > 1)
-            ptx::tma_load_2d_pair(stage + W_BYTES + X_BYTES + SFW_BYTES + 512, &maps.sfx, &ctl->full[s], 0,
-                                  sfx_atom + kt_count + kt);
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
-          PROF_ADD(1);
-        }
+        uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+        if (rank == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
+        __syncwarp();
+        if (lane < n_ops)
+          ptx::tma_load_2d_pair_hint(stage + my_off, my_map, &ctl->full[s], lane < 2 ? kt * TILE_K : 0,
+                                     lane < 2 ? my_c1 : my_c1 + kt, my_hint);
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+        PROF_ADD(1);
       }
+      if (!ok) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_PRODUCER);
+        }
+        break;
+      }
+    }
 #ifdef ES_PROFILE
+    if (lane == 0) {
       atomicAdd(&g_prof[0 + 4 * rank], (unsigned long long)_acc[0]);
       atomicAdd(&g_prof[1 + 4 * rank], (unsigned long long)_acc[1]);
       atomicAdd(&g_prof[2 + 4 * rank], (unsigned long long)_acc[2]);
-#endif
     }
+#endif
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue (leader CTA, one lane)
     if (lane == 0 && rank == 0) {
@@ -276,8 +287,11 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
             ptx::tc_cp_sf_pair(sfx_t + 4, ptx::make_desc_sf(stage + W_BYTES + X_BYTES + SFW_BYTES + 512));
           const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
           const uint64_t b_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
+#ifndef ES_EXPERIMENT
+#define ES_EXPERIMENT 0
+#endif
 #pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
+          for (uint32_t j = 0; j < ((ES_EXPERIMENT & 1) ? 0u : 4u); ++j) {
             ptx::tc_mma_mxf8_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
                                   ptx::make_idesc_mxf8(2 * TILE_N, ti.n_mma, j, j), sfw_t | (j << 30),
                                   (sfx_t + ti.sf_col) | (j << 30), (kt | j) != 0 ? 1u : 0u);
