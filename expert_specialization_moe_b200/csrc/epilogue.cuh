@@ -1,0 +1,51 @@
+// Accumulator -> global memory for the swap-AB grouped GEMM kernels.
+//
+// In TMEM the accumulator's lane is the output COLUMN n and its column is the token ROW, so a thread that reads its
+// lane with tcgen05.ld holds one n for many tokens — the transpose of what coalesced stores of d[token, n] want.
+// Each epilogue warp therefore passes 32 tokens x 32 n at a time through a private 2 KB shared-memory tile: written
+// as [token][n] with 2-byte stores (32 lanes = 64 contiguous bytes, conflict free), read back as 16-byte pieces of a
+// token row, and stored to global memory as 128-bit stores, four lanes per 64-byte row segment.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "sm100_ptx.cuh"
+
+namespace es_b200 {
+
+constexpr int EPI_STAGE_BYTES_PER_WARP = 32 * 32 * 2;
+
+template <typename OutT>
+__device__ __forceinline__ OutT out_from_f32(float v);
+template <>
+__device__ __forceinline__ __nv_bfloat16 out_from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ __half out_from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Drains `n_cols` accumulator columns (a multiple of 16) starting at TMEM address `taddr` (this warp's lane quadrant)
+// and stores the first `valid` of them: column j goes to dst[j * ld + 0..31] (dst = &d[first token][first n of warp]).
+// `release` is called once, right after the last TMEM read has completed (the accumulator may then be overwritten).
+template <typename OutT, class Release>
+__device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, int valid, OutT* stage_warp, OutT* dst,
+                                                  int64_t ld, bool do_store, int lane, Release release) {
+  for (int c0 = 0; c0 < n_cols; c0 += 32) {
+    uint32_t v[32];
+    ptx::tc_ld_32x32b_x32(taddr + c0, v);
+    ptx::tc_wait_ld();
+    if (c0 + 32 >= n_cols) release();
+    if (!do_store) continue;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) stage_warp[j * 32 + lane] = out_from_f32<OutT>(__uint_as_float(v[j]));
+    __syncwarp();
+    const int part = lane & 3;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int tok = it * 8 + (lane >> 2);
+      const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
+      if (c0 + tok < valid) *reinterpret_cast<uint4*>(dst + (int64_t)(c0 + tok) * ld + part * 8) = val;
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace es_b200

@@ -23,6 +23,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "epilogue.cuh"
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
@@ -56,7 +57,8 @@ struct SharedCtl {
   int tile_prefix[ES_B200_MAX_EXPERTS + 1];
 };
 
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(SharedCtl);
+constexpr size_t SMEM_BYTES =
+    1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + sizeof(SharedCtl);
 
 __device__ uint32_t g_status = 0;   // sticky error bits of the grouped GEMM kernels (bounded waits that gave up)
 
@@ -97,10 +99,11 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                         const __grid_constant__ CUtensorMap map_x128, const uint8_t* __restrict__ sf_tokens,
                         const uint8_t* __restrict__ sf_weights, OutT* __restrict__ d,
                         const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                        const int* __restrict__ blockscale_offsets, int num_experts, int n, int k) {
+                        const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int max_rows) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + (size_t)STAGES * STAGE_BYTES);
+  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 4 x 2 KB, one per epilogue warp
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + 4 * EPI_STAGE_BYTES_PER_WARP);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -128,9 +131,10 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   // everything above is independent of the previous kernel's output; problem sizes may not be
   pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
+  // experts with more than max_rows rows belong to the CTA-pair kernel
   block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
-    return m > 0 ? ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles : 0;
+    return (m > 0 && m <= max_rows) ? ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles : 0;
   });
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -232,23 +236,14 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       }
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-      OutT* dcol = d + (int64_t)ti.row0 * n + (ti.nt * TILE_N + q * 32 + lane);
-      for (int c0 = 0; c0 < ti.n_mma; c0 += 16) {
-        uint32_t v[16];
-        ptx::tc_ld_32x32b_x16(taddr + c0, v);
-        ptx::tc_wait_ld();
-        if (c0 + 16 >= ti.n_mma) {
-          // all of this warp's accumulator reads are done: hand the buffer back to the MMA warp
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
-        }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int tok = c0 + j;
-          if (tok < ti.valid) dcol[(int64_t)tok * n] = from_f32<OutT>(__uint_as_float(v[j]));
-        }
-      }
+      OutT* dst = d + (int64_t)ti.row0 * n + (ti.nt * TILE_N + q * 32);
+      drain_accumulator<OutT>(taddr, ti.n_mma, ti.valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, dst, n,
+                              true, lane, [&] {
+                                // all of this warp's accumulator reads are done: hand the buffer back to the MMA warp
+                                ptx::tc_fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+                              });
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
     }
@@ -264,7 +259,8 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 
 template <typename OutT>
 int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
-           const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, cudaStream_t stream) {
+           const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int max_rows,
+           cudaStream_t stream) {
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
@@ -301,7 +297,7 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sfa, sfb,
-                                 static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k));
+                                 static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, max_rows));
   return ES_B200_OK;
 }
 
@@ -309,9 +305,9 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
 
 namespace mm2 {   // CTA-pair kernel (mxfp8_grouped_mm_pair.cu)
 int launch_bf16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, cudaStream_t);
+                const int32_t*, int, int64_t, int, int, int64_t, int, cudaStream_t);
 int launch_fp16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, cudaStream_t);
+                const int32_t*, int, int64_t, int, int, int64_t, int, cudaStream_t);
 int read_and_clear_status(uint32_t* out);
 }  // namespace mm2
 namespace bw {    // FP8-blockwise kernel (fp8_blockwise_grouped_mm.cu)
@@ -337,30 +333,37 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
   if (num_experts == 0 || num_rows == 0) return ES_B200_OK;
   ES_REQUIRE(a && b && sfa && sfb && d && problem_sizes && expert_offsets && blockscale_offsets, "null pointer argument");
   ES_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sfa) && aligned16(sfb), "a, b, sfa, sfb must be 16-byte aligned");
-  ES_REQUIRE((reinterpret_cast<uintptr_t>(d) & 1u) == 0, "d must be 2-byte aligned");
+  ES_REQUIRE(aligned16(d), "d must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // Tile-shape specialisation by what the host knows without a device round trip (rows per expert on average):
-  // few rows per expert (decode) -> the layer streams weights, independent single CTAs with 128 x <=128 tiles keep
-  // the most bytes in flight; many rows per expert (prefill) -> CTA pairs with 256 x <=192 tiles halve the operand
-  // bytes per FLOP that each SM pulls through L2.  ES_B200_MM_KERNEL=single|pair overrides (for A/B measurements).
-  static const int forced = [] {
-    const char* v = getenv("ES_B200_MM_KERNEL");
-    return !v ? 0 : v[0] == 's' ? 1 : v[0] == 'p' ? 2 : 0;
+  // Tile-shape specialisation.  Problem sizes live on the device, so the host cannot bucket the experts; instead
+  // both specialised kernels are always launched, back to back on the caller's stream with programmatic dependent
+  // launch, and each one filters the experts by row count inside its own work-list scan:
+  //   rows <= threshold : single-CTA kernel, 128 weights x <=128 tokens, deep ring — these experts stream their
+  //                       weights from HBM exactly once, what counts is bytes in flight on every SM;
+  //   rows >  threshold : CTA-pair kernel, 256 weights x <=384 tokens, weight-stationary K step — these experts
+  //                       re-read operands from L2, what counts is operand bytes per FLOP.
+  // A kernel whose bucket is empty exits after its scan.  When even the host-known upper bound of rows per expert
+  // (num_rows) cannot reach the threshold, the pair kernel is not launched at all.
+  // ES_B200_MM_HEAVY_MIN_ROWS overrides the threshold (1 = everything on CTA pairs, 0 = never).
+  static const int threshold = [] {
+    const char* v = getenv("ES_B200_MM_HEAVY_MIN_ROWS");
+    return v ? atoi(v) : 129;
   }();
-  const bool use_pair = forced == 2 || (forced == 0 && num_rows >= (int64_t)32 * num_experts);
-  if (use_pair) {
-    ES_REQUIRE(sfa_rows >= 0, "sfa_rows must be non-negative");
-    if (out_dtype == ES_B200_BF16)
-      return mm2::launch_bf16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                              num_rows, n, k, sfa_rows, s);
-    return mm2::launch_fp16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                            num_rows, n, k, sfa_rows, s);
-  }
+  const int heavy_min = threshold <= 0 ? 0x7fffffff : threshold;
+  int rc;
   if (out_dtype == ES_B200_BF16)
-    return mm::launch<__nv_bfloat16>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                                     num_rows, n, k, s);
-  return mm::launch<__half>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows,
-                            n, k, s);
+    rc = mm::launch<__nv_bfloat16>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
+                                   num_rows, n, k, heavy_min - 1, s);
+  else
+    rc = mm::launch<__half>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows,
+                            n, k, heavy_min - 1, s);
+  if (rc != ES_B200_OK || num_rows < heavy_min) return rc;
+  ES_REQUIRE(sfa_rows >= 0, "sfa_rows must be non-negative");
+  if (out_dtype == ES_B200_BF16)
+    return mm2::launch_bf16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows,
+                            n, k, sfa_rows, heavy_min, s);
+  return mm2::launch_fp16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows, n,
+                          k, sfa_rows, heavy_min, s);
 }
 
 extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {

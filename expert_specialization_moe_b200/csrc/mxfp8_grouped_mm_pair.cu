@@ -1,23 +1,29 @@
-// MXFP8 block-scaled grouped GEMM for sm_100a on CTA PAIRS: tcgen05.mma.cta_group::2 with M = 256.
+// MXFP8 block-scaled grouped GEMM for sm_100a on CTA PAIRS, for experts with many token rows:
+// tcgen05.mma.cta_group::2 with M = 256 and a weight-stationary K step over up to 384 token rows.
 //
 // Same mapping as the single-CTA kernel (weights on the MMA M axis, the expert's token rows on the runtime-sized
-// MMA N axis), but two CTAs of a cluster share every tile: each CTA holds 128 of the 256 weight rows and HALF of
-// the token rows in its own shared memory, and the pair's tensor cores exchange the token halves.  Per CTA and
-// K step that is 16 KB of weights + at most 12 KB of tokens for a 128 x 192 x 128 share of the MMA, i.e. the
-// operand bytes each SM has to pull through L2 per FLOP are ~40 % lower than with 128 x 128 single-CTA tiles —
-// which is what bounds experts with many tokens — without any multicast load.  Token tiles are 192 rows: two
-// 192-column fp32 accumulators (double buffering) plus per-stage scale slots fit the 512 TMEM columns, and a
-// 192-row tile starts on a 64-row boundary of the 128-row scale atoms, which a 2-column TMEM offset addresses.
+// MMA N axis).  Two CTAs of a cluster share every work item: each CTA holds 128 of the 256 weight rows and HALF of
+// the token rows in its own shared memory, and the pair's tensor cores exchange the token halves (no multicast
+// load anywhere).  One work item covers up to 384 token rows as two sub-tiles of <=192 rows with one accumulator
+// each: every 16 KB weight stage that a CTA pulls through L2 feeds BOTH sub-tiles' MMAs.  Per CTA and K step that
+// is 16 KB of weights + 2 x 12 KB of tokens for 128 x 384 x 128 MACs — 2.4x fewer operand bytes per FLOP than
+// 128 x 128 single-CTA tiles, which is what bounds experts with many rows (the operand feed, not the tensor pipe).
+// Sub-tiles are 192 rows because two 192-column fp32 accumulators plus per-stage scale slots fit the 512 TMEM
+// columns, and the second sub-tile starts on a 64-row boundary of the 128-row scale atoms, which a TMEM column
+// offset addresses.
 //
-//   warp 0    producer (both CTAs): 4 TMA loads per K step (own weight rows, own half of the tokens, own weight
-//             scale atom, the tile's token scale atoms); all completion bytes are credited to the leader's barrier
+//   warp 0    producer (both CTAs): per K step lanes 0..6 each issue one TMA load (own weight rows, own halves of
+//             the two token sub-tiles, own weight scale atom, the item's token scale atoms); all completion bytes
+//             are credited to the leader CTA's barrier
 //   warp 1    TMEM allocation (both CTAs); in the leader CTA one lane issues tcgen05.cp (scales smem -> TMEM of
-//             both CTAs) and 4 tcgen05.mma per K step, and commits to the barriers of both CTAs
-//   warps 2-5 epilogue (both CTAs): own 128 accumulator lanes -> bf16/fp16 -> global
+//             both CTAs) and 4 + 4 tcgen05.mma per K step, and commits to the barriers of both CTAs
+//   warps 2-5 epilogue (both CTAs): own 128 accumulator lanes -> bf16/fp16 -> global, sub-tile 0 then sub-tile 1,
+//             so that the next item's first MMAs can start while the second accumulator is still being drained
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "epilogue.cuh"
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
@@ -27,17 +33,18 @@ namespace mm2 {
 constexpr int THREADS = 192;
 constexpr int TILE_N = 128;      // weight rows per CTA (the pair covers 256)
 constexpr int TILE_K = 128;
-constexpr int TOK_TILE = 192;    // token rows per tile (MMA N, runtime multiple of 16)
-constexpr int STAGES = 7;
+constexpr int SUB_TILE = 192;    // token rows per accumulator (MMA N, runtime multiple of 16)
+constexpr int TOK_TILE = 2 * SUB_TILE;   // token rows per work item
+constexpr int STAGES = 5;
 constexpr int W_BYTES = TILE_N * TILE_K;               // 16384
-constexpr int X_BYTES = (TOK_TILE / 2) * TILE_K;       // 12288: this CTA's half of the token tile
+constexpr int X_BYTES = (SUB_TILE / 2) * TILE_K;       // 12288: this CTA's half of one token sub-tile
 constexpr int SFW_BYTES = 512;
-constexpr int SFX_BYTES = 1024;                        // up to two 512-byte atoms
-constexpr int STAGE_BYTES = 30720;                     // 30 KB: W | X | SFW | SFX | pad  (multiple of 1024)
-static_assert(W_BYTES + X_BYTES + SFW_BYTES + SFX_BYTES <= STAGE_BYTES, "stage layout");
+constexpr int SFX_BYTES = 1536;                        // three 512-byte atoms cover 384 rows
+constexpr int STAGE_BYTES = 43008;                     // 42 KB: W | X0 | X1 | SFW | SFX  (multiple of 1024)
+static_assert(W_BYTES + 2 * X_BYTES + SFW_BYTES + SFX_BYTES <= STAGE_BYTES, "stage layout");
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ACC_COLS = 192;        // accumulators at columns [0,192) and [192,384)
-constexpr uint32_t SF_COL0 = 384;         // per-stage scale slots of 16 columns: 4 (weights) + 8 (tokens) + 4 unused
+constexpr uint32_t SF_COL0 = 384;         // per-stage scale slots of 16 columns: 4 (weights) + 12 (tokens)
 constexpr uint32_t SF_SLOT_COLS = 16;
 static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 
@@ -48,18 +55,18 @@ struct SharedCtl {
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];       // used in the leader CTA only (8 arrivals: 4 epilogue warps x 2 CTAs)
+                                // index = accumulator (sub-tile 0 / 1)
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
-  int tile_prefix[2][ES_B200_MAX_EXPERTS + 1];   // [0]: experts with one token tile (weights streamed once from HBM),
-                                                 // [1]: experts with several token tiles (weights re-read from L2)
+  int tile_prefix[ES_B200_MAX_EXPERTS + 1];
 #ifdef ES_PROFILE
   long long t_issue[STAGES];
   long long t_commit[STAGES];
 #endif
 };
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(SharedCtl);
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + sizeof(SharedCtl);
 
 __device__ uint32_t g_status = 0;
 #ifdef ES_PROFILE
@@ -73,43 +80,41 @@ __device__ unsigned long long g_prof[16];
 
 struct TileInfo {
   int e, tt, np;
-  int valid, n_mma;
-  int row0;        // first token row of the tile in a / d
-  int atom0;       // first 128-row scale atom of the tile inside the expert
-  int n_atoms;     // 1 or 2 atoms exist for this tile
-  uint32_t sf_col; // column offset of the tile's first row inside its first atom: 0 or 2
-  bool heavy;      // the expert has more than one token tile
+  int valid;       // token rows of this item that belong to the expert (<= 384)
+  int n0, n1;      // MMA N of the two sub-tiles (multiples of 16; n1 == 0 when the item has <= 192 rows)
+  int v0, v1;      // valid rows of the two sub-tiles
+  int row0;        // first token row of the item in a / d
+  int atom0;       // first 128-row scale atom of the item inside the expert (items start on atom boundaries)
+  int n_atoms;     // 1..3 atoms cover the item's valid rows
 };
 
-// Position p of the merged work list -> tile.  The two classes are merged proportionally (a Bresenham walk), so that
-// at any time the CTA pairs running side by side are a mix of HBM-streaming tiles and L2-resident, tensor-bound tiles
-// and both lists run out together.
-__device__ __forceinline__ TileInfo decode_tile(int p, const int (*prefix2)[ES_B200_MAX_EXPERTS + 1], int num_experts,
-                                                const int* problem_sizes, const int* expert_offsets) {
+__device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
+                                                const int* expert_offsets) {
   TileInfo ti;
-  const int n_light = prefix2[0][num_experts], n_heavy = prefix2[1][num_experts];
-  const long long tot = (long long)n_light + n_heavy;
-  const int h0 = (int)(((long long)p * n_heavy) / tot);
-  const int h1 = (int)(((long long)(p + 1) * n_heavy) / tot);
-  ti.heavy = h1 > h0;
-  const int t = ti.heavy ? h0 : p - h0;
-  const int* prefix = prefix2[ti.heavy ? 1 : 0];
   ti.e = upper_bound_expert(prefix, num_experts, t);
   const int i = t - prefix[ti.e];
   const int m = problem_sizes[ti.e * 3];
   const int token_tiles = (m + TOK_TILE - 1) / TOK_TILE;
   ti.np = i / token_tiles;
-  ti.tt = i - ti.np * token_tiles;
+  ti.tt = i - ti.np * token_tiles;     // token tile runs fastest: concurrent pairs share the weight slab in L2
   const int r_local = ti.tt * TOK_TILE;
   const int rem = m - r_local;
   ti.valid = rem < TOK_TILE ? rem : TOK_TILE;
-  ti.n_mma = (ti.valid + 15) & ~15;
+  ti.v0 = ti.valid < SUB_TILE ? ti.valid : SUB_TILE;
+  ti.v1 = ti.valid - ti.v0;
+  ti.n0 = (ti.v0 + 15) & ~15;
+  ti.n1 = (ti.v1 + 15) & ~15;
   ti.row0 = expert_offsets[ti.e] + r_local;
   ti.atom0 = r_local >> 7;
-  ti.sf_col = (uint32_t)((r_local & 127) >> 5);
-  const int last_atom = (r_local + ti.valid - 1) >> 7;
-  ti.n_atoms = last_atom - ti.atom0 + 1;
+  ti.n_atoms = (ti.valid + 127) >> 7;
   return ti;
+}
+
+__device__ __forceinline__ int box_index(int half_rows) {   // token tensor maps: boxes of 8 / 16 / 32 / 64 / 96 rows
+  return half_rows <= 8 ? 0 : half_rows <= 16 ? 1 : half_rows <= 32 ? 2 : half_rows <= 64 ? 3 : 4;
+}
+__device__ __forceinline__ uint32_t box_rows_of(int idx) {
+  return idx == 0 ? 8u : idx == 1 ? 16u : idx == 2 ? 32u : idx == 3 ? 64u : 96u;
 }
 
 template <typename OutT>
@@ -130,10 +135,11 @@ template <typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict__ d,
                              const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                             const int* __restrict__ blockscale_offsets, int num_experts, int n, int k) {
+                             const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + (size_t)STAGES * STAGE_BYTES);
+  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 4 x 2 KB, one per epilogue warp
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + 4 * EPI_STAGE_BYTES_PER_WARP);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
@@ -164,16 +170,17 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     ptx::tmem_alloc_pair(&ctl->tmem_base, TMEM_COLS);
     ptx::tmem_relinquish_pair();
   }
-  pdl_wait_prior_grid();
+  // This kernel is always launched right behind the single-CTA kernel of the same call, with programmatic dependent
+  // launch.  That kernel waited for everything before it (griddepcontrol.wait) before it let this one start, so the
+  // operands are final; the two kernels write disjoint rows of d.  This kernel therefore starts on SMs as they
+  // become free and only waits for its predecessor at the very end (below), which keeps stream order for whatever
+  // follows.
   const int n_tiles = n / TILE_N;
   const int n_pairs = (n_tiles + 1) >> 1;
-  block_exclusive_scan(num_experts, ctl->tile_prefix[0], ctl->warp_sums, [&](int e) {
+  // only experts with at least min_rows rows belong to this kernel (the single-CTA kernel takes the others)
+  block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
-    return (m > 0 && m <= TOK_TILE) ? n_pairs : 0;
-  });
-  block_exclusive_scan(num_experts, ctl->tile_prefix[1], ctl->warp_sums, [&](int e) {
-    const int m = problem_sizes[e * 3];
-    return m > TOK_TILE ? ((m + TOK_TILE - 1) / TOK_TILE) * n_pairs : 0;
+    return (m > 0 && m >= min_rows) ? ((m + TOK_TILE - 1) / TOK_TILE) * n_pairs : 0;
   });
   // barriers and TMEM of both CTAs must exist before either CTA signals the other
   ptx::tc_fence_before_sync();
@@ -182,7 +189,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   pdl_launch_dependents();
 
   const uint32_t tmem_base = ctl->tmem_base;
-  const int total_tiles = ctl->tile_prefix[0][num_experts] + ctl->tile_prefix[1][num_experts];
+  const int total_tiles = ctl->tile_prefix[num_experts];
   const int kt_count = k / TILE_K;
   const int sfw_atoms_per_expert = n_tiles * kt_count;
   volatile int* abort_flag = &ctl->abort_flag;
@@ -193,34 +200,34 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     // instruction (a TMA issue costs the issuing thread ~80 cycles, five in a row would be a third of a stage time).
     int s = 0;
     uint32_t ph = 0;
-    const bool mixed = ctl->tile_prefix[1][num_experts] > 0;
 #ifdef ES_PROFILE
     long long _acc[4] = {0, 0, 0, 0};
 #endif
     PROF_T0();
     for (int t = pair; t < total_tiles; t += num_pairs) {
       const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-      const int half = ti.n_mma >> 1;                       // token rows held by each CTA
-      const int xi = half <= 8 ? 0 : half <= 16 ? 1 : half <= 32 ? 2 : half <= 64 ? 3 : 4;
-      const uint32_t box_rows = xi == 0 ? 8u : xi == 1 ? 16u : xi == 2 ? 32u : xi == 3 ? 64u : 96u;
-      const uint32_t tx = 2u * (W_BYTES + box_rows * TILE_K + SFW_BYTES + (uint32_t)ti.n_atoms * 512u);
+      const int half0 = ti.n0 >> 1, half1 = ti.n1 >> 1;     // token rows of each sub-tile held by each CTA
+      const int xi0 = box_index(half0), xi1 = box_index(half1);
+      const uint32_t tx = 2u * (W_BYTES + box_rows_of(xi0) * TILE_K + (ti.n1 ? box_rows_of(xi1) * TILE_K : 0u) +
+                                SFW_BYTES + (uint32_t)ti.n_atoms * 512u);
       int nt = ti.np * 2 + (int)rank;
       const int w_row = ti.e * n + nt * TILE_N;             // may run past the expert when n/128 is odd: not stored
       if (nt >= n_tiles) nt = n_tiles - 1;                  // keep the scale-atom load inside the buffer
       const int sfw_atom = ti.e * sfw_atoms_per_expert + nt * kt_count;
       const int sfx_atom = ((blockscale_offsets[ti.e] >> 7) + ti.atom0) * kt_count;
-      const int x_row = ti.row0 + (int)rank * half;
-      // weights of single-tile experts are used once: do not let them push the re-read working set out of L2
-      const uint64_t w_hint = ti.heavy ? ptx::kL2EvictLast : (mixed ? ptx::kL2EvictFirst : ptx::kL2EvictNormal);
-      // this lane's load: 0 weights, 1 tokens, 2 weight scales, 3 / 4 token scale atoms
-      const int n_ops = 4 + (ti.n_atoms > 1 ? 1 : 0);
-      const CUtensorMap* my_map = lane == 0 ? &maps.w : lane == 1 ? &maps.x[xi] : lane == 2 ? &maps.sfw : &maps.sfx;
+      // this lane's load: 0 weights, 1 tokens of sub-tile 0, 2 tokens of sub-tile 1, 3 weight scales,
+      // 4..6 token scale atoms
+      const bool active = lane == 0 || lane == 1 || (lane == 2 && ti.n1 > 0) || lane == 3 ||
+                          (lane >= 4 && lane < 4 + ti.n_atoms);
+      const CUtensorMap* my_map = lane == 0 ? &maps.w : lane == 1 ? &maps.x[xi0] : lane == 2 ? &maps.x[xi1]
+                                  : lane == 3 ? &maps.sfw : &maps.sfx;
       const uint32_t my_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)W_BYTES : lane == 2 ? (uint32_t)(W_BYTES + X_BYTES)
-                              : lane == 3 ? (uint32_t)(W_BYTES + X_BYTES + SFW_BYTES)
-                                          : (uint32_t)(W_BYTES + X_BYTES + SFW_BYTES + 512);
-      const int my_c1 = lane == 0 ? w_row : lane == 1 ? x_row : lane == 2 ? sfw_atom : lane == 3 ? sfx_atom
-                                                                                               : sfx_atom + kt_count;
-      const uint64_t my_hint = lane == 0 ? w_hint : lane == 1 ? ptx::kL2EvictLast : ptx::kL2EvictNormal;
+                              : lane == 3 ? (uint32_t)(W_BYTES + 2 * X_BYTES)
+                                          : (uint32_t)(W_BYTES + 2 * X_BYTES + SFW_BYTES + (lane - 4) * 512);
+      const int my_c1 = lane == 0 ? w_row : lane == 1 ? ti.row0 + (int)rank * half0
+                        : lane == 2 ? ti.row0 + SUB_TILE + (int)rank * half1
+                        : lane == 3 ? sfw_atom : sfx_atom + (lane - 4) * kt_count;
+      const uint64_t my_hint = lane < 3 ? ptx::kL2EvictLast : ptx::kL2EvictNormal;
       bool ok = true;
       for (int kt = 0; kt < kt_count; ++kt) {
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag));
@@ -232,9 +239,9 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
         if (rank == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
         __syncwarp();
-        if (lane < n_ops)
-          ptx::tma_load_2d_pair_hint(stage + my_off, my_map, &ctl->full[s], lane < 2 ? kt * TILE_K : 0,
-                                     lane < 2 ? my_c1 : my_c1 + kt, my_hint);
+        if (active)
+          ptx::tma_load_2d_pair_hint(stage + my_off, my_map, &ctl->full[s], lane < 3 ? kt * TILE_K : 0,
+                                     lane < 3 ? my_c1 : my_c1 + kt, my_hint);
         if (++s == STAGES) { s = 0; ph ^= 1u; }
         PROF_ADD(1);
       }
@@ -258,8 +265,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     if (lane == 0 && rank == 0) {
       int s = 0;
       uint32_t ph = 0;
-      int acc = 0;
-      uint32_t acc_ph = 0;
+      uint32_t acc_ph[2] = {0, 0};     // phase of each accumulator's empty barrier (advances once per use)
       bool ok = true;
 #ifdef ES_PROFILE
       long long _acc[4] = {0, 0, 0, 0};
@@ -267,10 +273,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       PROF_T0();
       for (int t = pair; ok && t < total_tiles; t += num_pairs) {
         const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-        if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) ok = false;
-        PROF_ADD(0);
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        const uint32_t d0 = tmem_base, d1 = tmem_base + ACC_COLS;
         for (int kt = 0; ok && kt < kt_count; ++kt) {
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
           PROF_ADD(1);
@@ -281,20 +284,35 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
           const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
           const uint32_t sfw_t = tmem_base + SF_COL0 + s * SF_SLOT_COLS;
           const uint32_t sfx_t = sfw_t + 4;
-          ptx::tc_cp_sf_pair(sfw_t, ptx::make_desc_sf(stage + W_BYTES + X_BYTES));
-          ptx::tc_cp_sf_pair(sfx_t, ptx::make_desc_sf(stage + W_BYTES + X_BYTES + SFW_BYTES));
-          if (ti.n_atoms > 1)
-            ptx::tc_cp_sf_pair(sfx_t + 4, ptx::make_desc_sf(stage + W_BYTES + X_BYTES + SFW_BYTES + 512));
+          const uint32_t sf_smem = stage + W_BYTES + 2 * X_BYTES;
+          ptx::tc_cp_sf_pair(sfw_t, ptx::make_desc_sf(sf_smem));
+          for (int a = 0; a < ti.n_atoms; ++a)
+            ptx::tc_cp_sf_pair(sfx_t + 4 * a, ptx::make_desc_sf(sf_smem + SFW_BYTES + 512 * a));
           const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
-          const uint64_t b_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
-#ifndef ES_EXPERIMENT
-#define ES_EXPERIMENT 0
-#endif
+          const uint64_t b0_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
+          const uint64_t b1_desc = ptx::make_desc_k_sw128(stage + W_BYTES + X_BYTES);
+          if (kt == 0) {   // the previous item's epilogue must have drained accumulator 0
+            if (!ptx::mbar_wait(&ctl->tmem_empty[0], acc_ph[0] ^ 1u, abort_flag)) { ok = false; break; }
+            acc_ph[0] ^= 1u;
+            ptx::tc_fence_after_sync();
+            PROF_ADD(0);
+          }
 #pragma unroll
-          for (uint32_t j = 0; j < ((ES_EXPERIMENT & 1) ? 0u : 4u); ++j) {
-            ptx::tc_mma_mxf8_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j,
-                                  ptx::make_idesc_mxf8(2 * TILE_N, ti.n_mma, j, j), sfw_t | (j << 30),
-                                  (sfx_t + ti.sf_col) | (j << 30), (kt | j) != 0 ? 1u : 0u);
+          for (uint32_t j = 0; j < 4; ++j)
+            ptx::tc_mma_mxf8_pair(d0, a_desc + 2 * j, b0_desc + 2 * j, ptx::make_idesc_mxf8(2 * TILE_N, ti.n0, j, j),
+                                  sfw_t | (j << 30), sfx_t | (j << 30), (kt | j) != 0 ? 1u : 0u);
+          if (ti.n1 > 0) {
+            if (kt == 0) {
+              if (!ptx::mbar_wait(&ctl->tmem_empty[1], acc_ph[1] ^ 1u, abort_flag)) { ok = false; break; }
+              acc_ph[1] ^= 1u;
+              ptx::tc_fence_after_sync();
+              PROF_ADD(0);
+            }
+            // sub-tile 1 starts 192 rows = 6 scale columns into the item's scale block
+#pragma unroll
+            for (uint32_t j = 0; j < 4; ++j)
+              ptx::tc_mma_mxf8_pair(d1, a_desc + 2 * j, b1_desc + 2 * j, ptx::make_idesc_mxf8(2 * TILE_N, ti.n1, j, j),
+                                    sfw_t | (j << 30), (sfx_t + 6) | (j << 30), (kt | j) != 0 ? 1u : 0u);
           }
           ptx::tc_commit_pair(&ctl->empty[s], 3);       // both CTAs may refill the stage
 #ifdef ES_PROFILE
@@ -308,9 +326,8 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
           atomicOr(&g_status, ERR_MMA);
           break;
         }
-        ptx::tc_commit_pair(&ctl->tmem_full[acc], 3);   // accumulators of both CTAs complete
-        acc ^= 1;
-        if (acc == 0) acc_ph ^= 1u;
+        ptx::tc_commit_pair(&ctl->tmem_full[0], 3);     // accumulators of both CTAs complete
+        if (ti.n1 > 0) ptx::tc_commit_pair(&ctl->tmem_full[1], 3);
       }
 #ifdef ES_PROFILE
       atomicAdd(&g_prof[8], (unsigned long long)_acc[0]);
@@ -323,42 +340,35 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
     const int q = warp & 3;
-    int acc = 0;
-    uint32_t acc_ph = 0;
-    for (int t = pair; t < total_tiles; t += num_pairs) {
+    uint32_t full_ph[2] = {0, 0};
+    bool alive = true;
+    for (int t = pair; alive && t < total_tiles; t += num_pairs) {
       const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-      const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) {
-          *abort_flag = 1;
-          atomicOr(&g_status, ERR_EPILOGUE);
-        }
-        break;
-      }
-      ptx::tc_fence_after_sync();
       const int nt = ti.np * 2 + (int)rank;
       const bool store = nt < n_tiles;
-      const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-      OutT* dcol = d + (int64_t)ti.row0 * n + (nt * TILE_N + q * 32 + lane);
-      for (int c0 = 0; c0 < ti.n_mma; c0 += 16) {
-        uint32_t v[16];
-        ptx::tc_ld_32x32b_x16(taddr + c0, v);
-        ptx::tc_wait_ld();
-        if (c0 + 16 >= ti.n_mma) {
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[acc], 0);   // the leader owns this barrier
-        }
-        if (store) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int tok = c0 + j;
-            if (tok < ti.valid) dcol[(int64_t)tok * n] = from_f32<OutT>(__uint_as_float(v[j]));
+      for (int sub = 0; sub < (ti.n1 > 0 ? 2 : 1); ++sub) {
+        const int n_mma = sub == 0 ? ti.n0 : ti.n1;
+        const int valid = sub == 0 ? ti.v0 : ti.v1;
+        const bool got = ptx::mbar_wait(&ctl->tmem_full[sub], full_ph[sub], abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            atomicOr(&g_status, ERR_EPILOGUE);
           }
+          alive = false;
+          break;
         }
+        full_ph[sub] ^= 1u;
+        ptx::tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + sub * ACC_COLS + ((uint32_t)(q * 32) << 16);
+        OutT* dst = d + (int64_t)(ti.row0 + sub * SUB_TILE) * n + (nt * TILE_N + q * 32);
+        drain_accumulator<OutT>(taddr, n_mma, valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, dst, n,
+                                store, lane, [&] {
+                                  ptx::tc_fence_before_sync();
+                                  __syncwarp();
+                                  if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[sub], 0);   // leader's barrier
+                                });
       }
-      acc ^= 1;
-      if (acc == 0) acc_ph ^= 1u;
     }
   }
 
@@ -369,12 +379,13 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     __syncwarp();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+  pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has completed
 }
 
 template <typename OutT>
 int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
            const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int64_t sfa_rows,
-           cudaStream_t stream) {
+           int min_rows, cudaStream_t stream) {
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
@@ -432,19 +443,19 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   const int clusters = (int)(max_tiles < max_clusters ? max_tiles : max_clusters);
   cfg.gridDim = dim3(2 * clusters);
   cfg.numAttrs = 2;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k));
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows));
   return ES_B200_OK;
 }
 
 int launch_bf16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
                 const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, cudaStream_t stream) {
-  return launch<__nv_bfloat16>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, stream);
+                int64_t sfa_rows, int min_rows, cudaStream_t stream) {
+  return launch<__nv_bfloat16>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows, stream);
 }
 int launch_fp16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
                 const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, cudaStream_t stream) {
-  return launch<__half>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, stream);
+                int64_t sfa_rows, int min_rows, cudaStream_t stream) {
+  return launch<__half>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows, stream);
 }
 
 #ifdef ES_PROFILE
