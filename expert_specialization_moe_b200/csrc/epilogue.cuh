@@ -28,23 +28,36 @@ __device__ __forceinline__ __half out_from_f32<__half>(float v) { return __float
 template <typename OutT, class Release>
 __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, int valid, OutT* stage_warp, OutT* dst,
                                                   int64_t ld, bool do_store, int lane, Release release) {
-  for (int c0 = 0; c0 < n_cols; c0 += 32) {
-    uint32_t v[32];
-    ptx::tc_ld_32x32b_x32(taddr + c0, v);
-    ptx::tc_wait_ld();
-    if (c0 + 32 >= n_cols) release();
-    if (!do_store) continue;
+  // two register sets: the TMEM read of chunk c+1 is in flight while chunk c goes through shared memory
+  uint32_t va[32], vb[32];
+  ptx::tc_ld_32x32b_x32(taddr, va);
+  const int part = lane & 3;
+  for (int c0 = 0; c0 < n_cols; c0 += 64) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) stage_warp[j * 32 + lane] = out_from_f32<OutT>(__uint_as_float(v[j]));
-    __syncwarp();
-    const int part = lane & 3;
+    for (int h = 0; h < 2; ++h) {
+      const int c = c0 + h * 32;
+      if (c >= n_cols) break;
+      ptx::tc_wait_ld();                                    // chunk c is in registers (va if h == 0, vb otherwise)
+      const bool more = c + 32 < n_cols;
+      if (more) {
+        if (h == 0) ptx::tc_ld_32x32b_x32(taddr + c + 32, vb); else ptx::tc_ld_32x32b_x32(taddr + c + 32, va);
+      } else {
+        release();
+      }
+      if (do_store) {
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int tok = it * 8 + (lane >> 2);
-      const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
-      if (c0 + tok < valid) *reinterpret_cast<uint4*>(dst + (int64_t)(c0 + tok) * ld + part * 8) = val;
+        for (int j = 0; j < 32; ++j)
+          stage_warp[j * 32 + lane] = out_from_f32<OutT>(__uint_as_float(h == 0 ? va[j] : vb[j]));
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int tok = it * 8 + (lane >> 2);
+          const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
+          if (c + tok < valid) *reinterpret_cast<uint4*>(dst + (int64_t)(c + tok) * ld + part * 8) = val;
+        }
+        __syncwarp();
+      }
     }
-    __syncwarp();
   }
 }
 

@@ -285,9 +285,11 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
           const uint32_t sfw_t = tmem_base + SF_COL0 + s * SF_SLOT_COLS;
           const uint32_t sfx_t = sfw_t + 4;
           const uint32_t sf_smem = stage + W_BYTES + 2 * X_BYTES;
+          // scale copies: sub-tile 0 (rows 0..191) needs token atoms 0 and 1, sub-tile 1 (rows 192..383) atoms 1
+          // and 2; the third atom's copy is issued behind sub-tile 0's MMAs, which do not depend on it
           ptx::tc_cp_sf_pair(sfw_t, ptx::make_desc_sf(sf_smem));
-          for (int a = 0; a < ti.n_atoms; ++a)
-            ptx::tc_cp_sf_pair(sfx_t + 4 * a, ptx::make_desc_sf(sf_smem + SFW_BYTES + 512 * a));
+          ptx::tc_cp_sf_pair(sfx_t, ptx::make_desc_sf(sf_smem + SFW_BYTES));
+          if (ti.n_atoms > 1) ptx::tc_cp_sf_pair(sfx_t + 4, ptx::make_desc_sf(sf_smem + SFW_BYTES + 512));
           const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
           const uint64_t b0_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
           const uint64_t b1_desc = ptx::make_desc_k_sw128(stage + W_BYTES + X_BYTES);
@@ -302,6 +304,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
             ptx::tc_mma_mxf8_pair(d0, a_desc + 2 * j, b0_desc + 2 * j, ptx::make_idesc_mxf8(2 * TILE_N, ti.n0, j, j),
                                   sfw_t | (j << 30), sfx_t | (j << 30), (kt | j) != 0 ? 1u : 0u);
           if (ti.n1 > 0) {
+            if (ti.n_atoms > 2) ptx::tc_cp_sf_pair(sfx_t + 8, ptx::make_desc_sf(sf_smem + SFW_BYTES + 1024));
             if (kt == 0) {
               if (!ptx::mbar_wait(&ctl->tmem_empty[1], acc_ph[1] ^ 1u, abort_flag)) { ok = false; break; }
               acc_ph[1] ^= 1u;
