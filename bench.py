@@ -432,8 +432,9 @@ def main():
     elapsed_ms, e2e_ms = float(stats[0]), float(stats[1])
     flops_total, h2d_total, d2h_total = float(sums[0]), float(sums[1]), float(sums[2])
 
-    # the op launches the single-CTA kernel always and the CTA-pair kernel whenever the row count can reach its bucket
-    launches_per_step = 2 if int(counts.sum()) >= 129 else 1
+    # one call launches one kernel per row-count bucket that the host-known row count can reach:
+    # <=32 rows (always), 33..128 rows, >=129 rows (CTA pairs)
+    launches_per_step = 1 + (int(counts.sum()) > 32) + (int(counts.sum()) >= 129)
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
         value = flops_total / (ms_per_step * 1e-3) / 1e12
@@ -450,8 +451,9 @@ def main():
             "config": config,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": peak_kind, "algorithmic_bytes": abytes,
-                         "kernel": ("mxfp8_grouped_mm_kernel + mxfp8_grouped_mm_pair_kernel (one PDL chain per call)"
-                                    if launches_per_step == 2 else "mxfp8_grouped_mm_kernel"), "kernel_ms": my_ms},
+                         "kernel": ("mxfp8_grouped_mm_kernel<32x10> + <128x6> + mxfp8_grouped_mm_pair_kernel "
+                                    "(one PDL chain per call)" if launches_per_step == 3 else "mxfp8_grouped_mm_kernel"),
+                         "kernel_ms": my_ms},
             "clocks": clocks, "gpu_launches": args.steps * launches_per_step,
         }
         if e2e:

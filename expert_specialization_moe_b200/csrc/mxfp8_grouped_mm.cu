@@ -33,12 +33,24 @@ namespace mm {
 constexpr int THREADS = 192;
 constexpr int TILE_N = 128;     // weight rows per tile  (tcgen05.mma M)
 constexpr int TILE_K = 128;     // bytes of K per pipeline stage (one 128-byte swizzle atom)
-constexpr int TOK_TILE = 128;   // token rows per tile   (tcgen05.mma N, runtime multiple of 16)
-constexpr int STAGES = 6;
 constexpr int W_BYTES = TILE_N * TILE_K;
-constexpr int X_BYTES = TOK_TILE * TILE_K;
 constexpr int SF_BYTES = 512;
-constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // 33792, a multiple of 1024
+constexpr int MAX_STAGES = 10;
+
+// Two tile shapes of the same kernel.  What bounds a streaming expert is how many weight bytes each SM keeps in
+// flight, i.e. the number of ring stages that fit the 227 KB of shared memory: experts with at most 32 rows need a
+// 4 KB token slot per stage and get 10 stages (160 KB of weights in flight), experts with up to 128 rows a 16 KB
+// slot and 6 stages.
+template <int TOK_TILE_, int STAGES_>
+struct Shape {
+  static constexpr int TOK_TILE = TOK_TILE_;     // token rows per tile (tcgen05.mma N, runtime multiple of 16)
+  static constexpr int STAGES = STAGES_;
+  static constexpr int X_BYTES = TOK_TILE * TILE_K;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // a multiple of 1024
+  static_assert(STAGE_BYTES % 1024 == 0 && STAGES <= MAX_STAGES, "stage layout");
+};
+using ShapeTiny = Shape<32, 10>;     // 21 KB stages
+using ShapeMid = Shape<128, 6>;      // 33 KB stages
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t ACC_COLS = 128;      // two accumulators: columns [0,128) and [128,256)
 constexpr uint32_t SFW_COL = 256;       // 4 columns: scales of the weight tile
@@ -47,8 +59,8 @@ constexpr uint32_t SFX_COL = 260;       // 4 columns: scales of the token tile
 constexpr uint32_t ERR_PRODUCER = 1u, ERR_MMA = 2u, ERR_EPILOGUE = 4u;
 
 struct SharedCtl {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -57,8 +69,10 @@ struct SharedCtl {
   int tile_prefix[ES_B200_MAX_EXPERTS + 1];
 };
 
-constexpr size_t SMEM_BYTES =
-    1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + sizeof(SharedCtl);
+template <class S>
+constexpr size_t smem_bytes() {
+  return 1024 /*alignment slack*/ + (size_t)S::STAGES * S::STAGE_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + sizeof(SharedCtl);
+}
 
 __device__ uint32_t g_status = 0;   // sticky error bits of the grouped GEMM kernels (bounded waits that gave up)
 
@@ -69,6 +83,7 @@ struct TileInfo {
   int row0;      // first token row in a / d
 };
 
+template <int TOK_TILE>
 __device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
                                                 const int* expert_offsets) {
   TileInfo ti;
@@ -92,14 +107,16 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { retu
 template <>
 __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
-template <typename OutT>
+template <typename OutT, class S>
 __global__ void __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
                         const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
                         const __grid_constant__ CUtensorMap map_x128, const uint8_t* __restrict__ sf_tokens,
                         const uint8_t* __restrict__ sf_weights, OutT* __restrict__ d,
                         const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                        const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int max_rows) {
+                        const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
+                        int max_rows, int wait_at_start) {
+  constexpr int TOK_TILE = S::TOK_TILE, STAGES = S::STAGES, X_BYTES = S::X_BYTES, STAGE_BYTES = S::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 4 x 2 KB, one per epilogue warp
@@ -128,13 +145,16 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     ptx::tmem_alloc(&ctl->tmem_base, TMEM_COLS);
     ptx::tmem_relinquish();
   }
-  // everything above is independent of the previous kernel's output; problem sizes may not be
-  pdl_wait_prior_grid();
+  // Everything above is independent of the previous kernel's output; problem sizes may not be.  The first kernel
+  // of a call waits here for whatever precedes the call; the later kernels of the same call are launched (programmatic
+  // dependent launch) only after every CTA of the first has passed this point, so their operands are final: they
+  // start on SMs as they become free and wait for their predecessor only before they exit.
+  if (wait_at_start) pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
-  // experts with more than max_rows rows belong to the CTA-pair kernel
+  // this launch owns the experts with min_rows <= rows <= max_rows
   block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
-    return (m > 0 && m <= max_rows) ? ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles : 0;
+    return (m > 0 && m >= min_rows && m <= max_rows) ? ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles : 0;
   });
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -154,7 +174,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_x128;
         const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : 128u;
         const uint32_t tx = W_BYTES + box_rows * TILE_K + 2 * SF_BYTES;
@@ -189,7 +209,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       const uint32_t sfw_t = tmem_base + SFW_COL;
       const uint32_t sfx_t = tmem_base + SFX_COL;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) { ok = false; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
@@ -225,7 +245,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     int acc = 0;
     uint32_t acc_ph = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
       const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) {
@@ -255,12 +275,15 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     __syncwarp();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
 }
 
-template <typename OutT>
+template <typename OutT, class S>
 int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
-           const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int max_rows,
-           cudaStream_t stream) {
+           const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int min_rows,
+           int max_rows, bool first_of_call, cudaStream_t stream) {
+  constexpr int TOK_TILE = S::TOK_TILE;
+  constexpr size_t SMEM_BYTES = smem_bytes<S>();
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
@@ -274,7 +297,7 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
     if (rc != ES_B200_OK) return rc;
   }
 
-  auto kernel = mxfp8_grouped_mm_kernel<OutT>;
+  auto kernel = mxfp8_grouped_mm_kernel<OutT, S>;
   static bool configured[64] = {false};   // per device (one static per instantiation)
   int dev = 0;
   ES_CUDA_TRY(cudaGetDevice(&dev));
@@ -297,7 +320,8 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sfa, sfb,
-                                 static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, max_rows));
+                                 static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows, max_rows,
+                                 first_of_call ? 1 : 0));
   return ES_B200_OK;
 }
 
@@ -305,9 +329,9 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
 
 namespace mm2 {   // CTA-pair kernel (mxfp8_grouped_mm_pair.cu)
 int launch_bf16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, int, cudaStream_t);
+                const int32_t*, int, int64_t, int, int, int64_t, int, int, cudaStream_t);
 int launch_fp16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, int, cudaStream_t);
+                const int32_t*, int, int64_t, int, int, int64_t, int, int, cudaStream_t);
 int read_and_clear_status(uint32_t* out);
 }  // namespace mm2
 namespace bw {    // FP8-blockwise kernel (fp8_blockwise_grouped_mm.cu)
@@ -338,32 +362,49 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
   // Tile-shape specialisation.  Problem sizes live on the device, so the host cannot bucket the experts; instead
   // both specialised kernels are always launched, back to back on the caller's stream with programmatic dependent
   // launch, and each one filters the experts by row count inside its own work-list scan:
-  //   rows <= threshold : single-CTA kernel, 128 weights x <=128 tokens, deep ring — these experts stream their
-  //                       weights from HBM exactly once, what counts is bytes in flight on every SM;
+  //   rows <= 32        : single-CTA kernel, 128 weights x <=32 tokens, 10-stage ring  \  these experts stream their
+  //   rows <= threshold : single-CTA kernel, 128 weights x <=128 tokens, 6-stage ring  /  weights from HBM exactly
+  //                       once; what counts is weight bytes in flight on every SM;
   //   rows >  threshold : CTA-pair kernel, 256 weights x <=384 tokens, weight-stationary K step — these experts
   //                       re-read operands from L2, what counts is operand bytes per FLOP.
-  // A kernel whose bucket is empty exits after its scan.  When even the host-known upper bound of rows per expert
-  // (num_rows) cannot reach the threshold, the pair kernel is not launched at all.
+  // A kernel whose bucket is empty exits after its scan.  A bucket that even the host-known upper bound of rows per
+  // expert (num_rows) cannot reach is not launched at all.
   // ES_B200_MM_HEAVY_MIN_ROWS overrides the threshold (1 = everything on CTA pairs, 0 = never).
   static const int threshold = [] {
     const char* v = getenv("ES_B200_MM_HEAVY_MIN_ROWS");
     return v ? atoi(v) : 129;
   }();
   const int heavy_min = threshold <= 0 ? 0x7fffffff : threshold;
-  int rc;
-  if (out_dtype == ES_B200_BF16)
-    rc = mm::launch<__nv_bfloat16>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                                   num_rows, n, k, heavy_min - 1, s);
-  else
-    rc = mm::launch<__half>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows,
-                            n, k, heavy_min - 1, s);
-  if (rc != ES_B200_OK || num_rows < heavy_min) return rc;
+  const int tiny_max = heavy_min - 1 < 32 ? heavy_min - 1 : 32;
+  const bool bf16 = out_dtype == ES_B200_BF16;
+  int rc = ES_B200_OK;
+  bool first = true;
+  // <= 32 rows: 128 x <=32 tiles, 10-stage ring
+  if (tiny_max >= 1) {
+    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeTiny>(a, b, sfa, sfb, d, problem_sizes, expert_offsets,
+                                                         blockscale_offsets, num_experts, num_rows, n, k, 1, tiny_max,
+                                                         first, s)
+              : mm::launch<__half, mm::ShapeTiny>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets,
+                                                  num_experts, num_rows, n, k, 1, tiny_max, first, s);
+    if (rc != ES_B200_OK) return rc;
+    first = false;
+  }
+  // 33 .. heavy_min-1 rows: 128 x <=128 tiles, 6-stage ring
+  if (heavy_min - 1 > tiny_max && num_rows > tiny_max) {
+    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeMid>(a, b, sfa, sfb, d, problem_sizes, expert_offsets,
+                                                        blockscale_offsets, num_experts, num_rows, n, k, tiny_max + 1,
+                                                        heavy_min - 1, first, s)
+              : mm::launch<__half, mm::ShapeMid>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets,
+                                                 num_experts, num_rows, n, k, tiny_max + 1, heavy_min - 1, first, s);
+    if (rc != ES_B200_OK) return rc;
+    first = false;
+  }
+  if (num_rows < heavy_min) return rc;
   ES_REQUIRE(sfa_rows >= 0, "sfa_rows must be non-negative");
-  if (out_dtype == ES_B200_BF16)
-    return mm2::launch_bf16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows,
-                            n, k, sfa_rows, heavy_min, s);
-  return mm2::launch_fp16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows, n,
-                          k, sfa_rows, heavy_min, s);
+  return bf16 ? mm2::launch_bf16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
+                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, s)
+              : mm2::launch_fp16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
+                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, s);
 }
 
 extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {

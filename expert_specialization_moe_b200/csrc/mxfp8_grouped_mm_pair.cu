@@ -135,7 +135,8 @@ template <typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict__ d,
                              const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                             const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows) {
+                             const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
+                             int wait_at_start) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 4 x 2 KB, one per epilogue warp
@@ -170,11 +171,12 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     ptx::tmem_alloc_pair(&ctl->tmem_base, TMEM_COLS);
     ptx::tmem_relinquish_pair();
   }
-  // This kernel is always launched right behind the single-CTA kernel of the same call, with programmatic dependent
-  // launch.  That kernel waited for everything before it (griddepcontrol.wait) before it let this one start, so the
-  // operands are final; the two kernels write disjoint rows of d.  This kernel therefore starts on SMs as they
-  // become free and only waits for its predecessor at the very end (below), which keeps stream order for whatever
-  // follows.
+  // Normally this kernel is launched behind the single-CTA kernels of the same call, with programmatic dependent
+  // launch.  The first kernel of the call waited for everything before it (griddepcontrol.wait) before it let the
+  // others start, so the operands are final; the kernels write disjoint rows of d.  This kernel therefore starts on
+  // SMs as they become free and only waits for its predecessor at the very end (below), which keeps stream order for
+  // whatever follows.  When it is the only kernel of the call it waits up front like any first kernel.
+  if (wait_at_start) pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
   const int n_pairs = (n_tiles + 1) >> 1;
   // only experts with at least min_rows rows belong to this kernel (the single-CTA kernel takes the others)
@@ -382,13 +384,13 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     __syncwarp();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
-  pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has completed
+  if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
 }
 
 template <typename OutT>
 int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
            const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int64_t sfa_rows,
-           int min_rows, cudaStream_t stream) {
+           int min_rows, int wait_at_start, cudaStream_t stream) {
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
@@ -446,19 +448,21 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   const int clusters = (int)(max_tiles < max_clusters ? max_tiles : max_clusters);
   cfg.gridDim = dim3(2 * clusters);
   cfg.numAttrs = 2;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows));
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows, wait_at_start));
   return ES_B200_OK;
 }
 
 int launch_bf16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
                 const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, int min_rows, cudaStream_t stream) {
-  return launch<__nv_bfloat16>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows, stream);
+                int64_t sfa_rows, int min_rows, int wait_at_start, cudaStream_t stream) {
+  return launch<__nv_bfloat16>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows,
+                               wait_at_start, stream);
 }
 int launch_fp16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
                 const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, int min_rows, cudaStream_t stream) {
-  return launch<__half>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows, stream);
+                int64_t sfa_rows, int min_rows, int wait_at_start, cudaStream_t stream) {
+  return launch<__half>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows, wait_at_start,
+                        stream);
 }
 
 #ifdef ES_PROFILE
