@@ -12,4 +12,5 @@ from .ops import (  # noqa: F401
     es_fp8_blockwise_scaled_grouped_mm,
     es_sm100_mxfp8_blockscaled_grouped_mm,
     es_sm100_mxfp8_blockscaled_grouped_quant,
+    es_sm100_mxfp8_silu_mul_grouped_quant,
 )

@@ -27,6 +27,8 @@ def _declare(lib):
     lib.es_b200_mxfp8_grouped_quant.restype = c_int
     lib.es_b200_mxfp8_grouped_quant.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_int, c_int64, c_int, c_void_p]
+    lib.es_b200_mxfp8_silu_mul_grouped_quant.restype = c_int
+    lib.es_b200_mxfp8_silu_mul_grouped_quant.argtypes = lib.es_b200_mxfp8_grouped_quant.argtypes
     lib.es_b200_grouped_mm_scratch_bytes.restype = c_size_t
     lib.es_b200_grouped_mm_scratch_bytes.argtypes = [c_int, c_int64, c_int, c_int]
     lib.es_b200_mxfp8_grouped_mm.restype = c_int

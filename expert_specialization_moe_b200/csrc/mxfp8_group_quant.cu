@@ -49,12 +49,14 @@ struct Vec2<__nv_bfloat16> {
   using type = __nv_bfloat162;
   static __device__ __forceinline__ float2 to_float2(type v) { return __bfloat1622float2(v); }
   static __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ type from_floats(float a, float b) { return __floats2bfloat162_rn(a, b); }
 };
 template <>
 struct Vec2<__half> {
   using type = __half2;
   static __device__ __forceinline__ float2 to_float2(type v) { return __half22float2(v); }
   static __device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ type from_floats(float a, float b) { return __floats2half2_rn(a, b); }
 };
 
 // Quantise the 8 elements this lane holds; the four lanes of a quad share one 32-element block.
@@ -98,7 +100,27 @@ __device__ __forceinline__ uint32_t quantize8(const uint4& raw, uint2& codes) {
   return sf.__x;
 }
 
+// act = round_to_T( silu(gate) * up ) on 8 elements, computed in fp32: x / (1 + exp(-x)) with the accurate expf, one
+// IEEE multiply, round to nearest even — the arithmetic of an unfused silu(gate.float()) * up.float() -> T.
 template <typename T>
+__device__ __forceinline__ uint4 silu_mul8(const uint4& g, const uint4& u) {
+  using V2 = typename Vec2<T>::type;
+  const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+  uint32_t out[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 gf = Vec2<T>::to_float2(*reinterpret_cast<const V2*>(&gw[i]));
+    const float2 uf = Vec2<T>::to_float2(*reinterpret_cast<const V2*>(&uw[i]));
+    const float a0 = (gf.x / (1.0f + expf(-gf.x))) * uf.x;
+    const float a1 = (gf.y / (1.0f + expf(-gf.y))) * uf.y;
+    const V2 r = Vec2<T>::from_floats(a0, a1);
+    out[i] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// kSiluMul = false: input [rows, k].  kSiluMul = true: input [rows, 2k] = gate | up, quantises silu(gate) * up.
+template <typename T, bool kSiluMul>
 __global__ void __launch_bounds__(QUANT_THREADS)
 mxfp8_group_quant_kernel(const T* __restrict__ input, const int* __restrict__ problem_sizes,
                          const int* __restrict__ expert_offsets, const int* __restrict__ blockscale_offsets,
@@ -129,7 +151,7 @@ mxfp8_group_quant_kernel(const T* __restrict__ input, const int* __restrict__ pr
 
     if (r < m) {
       const int64_t grow = (int64_t)expert_offsets[e] + r;
-      const T* in_row = input + grow * k;
+      const T* in_row = input + grow * (kSiluMul ? 2 * (int64_t)k : (int64_t)k);
       uint8_t* out_row = quant_output + grow * k;
       // scale word of (row r, K tile q): atom (r/128, q), inside the atom (r%32)*16 + ((r%128)/32)*4
       uint8_t* sf_row = sf_expert + (int64_t)(r >> 7) * kt * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4;
@@ -140,6 +162,16 @@ mxfp8_group_quant_kernel(const T* __restrict__ input, const int* __restrict__ pr
         for (int j = 0; j < QUANT_UNROLL; ++j) {
           const int col = c0 + j * 256 + lane * 8;
           raw[j] = col < k ? ld_stream_16B(in_row + col) : make_uint4(0, 0, 0, 0);
+        }
+        if constexpr (kSiluMul) {
+          uint4 up[QUANT_UNROLL];
+#pragma unroll
+          for (int j = 0; j < QUANT_UNROLL; ++j) {
+            const int col = c0 + j * 256 + lane * 8;
+            up[j] = col < k ? ld_stream_16B(in_row + k + col) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int j = 0; j < QUANT_UNROLL; ++j) raw[j] = silu_mul8<T>(raw[j], up[j]);
         }
 #pragma unroll
         for (int j = 0; j < QUANT_UNROLL; ++j) {
@@ -175,13 +207,10 @@ mxfp8_group_quant_kernel(const T* __restrict__ input, const int* __restrict__ pr
   }
 }
 
-}  // namespace es_b200
-
-extern "C" int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, const int32_t* problem_sizes,
-                                           const int32_t* expert_offsets, const int32_t* blockscale_offsets,
-                                           void* quant_output, uint8_t* scale_factor, int num_experts,
-                                           int64_t num_rows, int k, void* stream) {
-  using namespace es_b200;
+template <bool kSiluMul>
+static int quant_impl(const void* input, int input_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
+                      const int32_t* blockscale_offsets, void* quant_output, uint8_t* scale_factor, int num_experts,
+                      int64_t num_rows, int k, void* stream) {
   ES_REQUIRE(input_dtype == ES_B200_BF16 || input_dtype == ES_B200_FP16, "dtype must be kFloat16 or kBFloat16");
   ES_REQUIRE(k > 0 && k % 128 == 0, "k must align to 128");
   ES_REQUIRE(num_experts >= 0 && num_experts <= ES_B200_MAX_EXPERTS,
@@ -199,14 +228,14 @@ extern "C" int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, c
 
   // at most one partial chunk per expert on top of the full chunks of num_rows rows
   const int64_t max_chunks = (num_rows + QUANT_ROWS_PER_CHUNK - 1) / QUANT_ROWS_PER_CHUNK + num_experts;
-  static int blocks_per_sm[2] = {0, 0};   // per input type; the kernel's occupancy does not depend on the device here
+  static int blocks_per_sm[2] = {0, 0};   // per input type (and per instantiation); same on every device of a box
   int& occ = blocks_per_sm[input_dtype == ES_B200_BF16 ? 0 : 1];
   if (occ == 0) {
     int v = 0;
     if (input_dtype == ES_B200_BF16)
-      ES_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, mxfp8_group_quant_kernel<__nv_bfloat16>, QUANT_THREADS, 0));
+      ES_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, mxfp8_group_quant_kernel<__nv_bfloat16, kSiluMul>, QUANT_THREADS, 0));
     else
-      ES_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, mxfp8_group_quant_kernel<__half>, QUANT_THREADS, 0));
+      ES_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, mxfp8_group_quant_kernel<__half, kSiluMul>, QUANT_THREADS, 0));
     occ = v > 0 ? v : 1;
   }
   const int64_t resident = (int64_t)info.sm_count * occ;
@@ -214,14 +243,31 @@ extern "C" int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, c
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (input_dtype == ES_B200_BF16) {
-    mxfp8_group_quant_kernel<__nv_bfloat16><<<grid, QUANT_THREADS, 0, s>>>(
+    mxfp8_group_quant_kernel<__nv_bfloat16, kSiluMul><<<grid, QUANT_THREADS, 0, s>>>(
         static_cast<const __nv_bfloat16*>(input), problem_sizes, expert_offsets, blockscale_offsets,
         static_cast<uint8_t*>(quant_output), scale_factor, num_experts, k);
   } else {
-    mxfp8_group_quant_kernel<__half><<<grid, QUANT_THREADS, 0, s>>>(
+    mxfp8_group_quant_kernel<__half, kSiluMul><<<grid, QUANT_THREADS, 0, s>>>(
         static_cast<const __half*>(input), problem_sizes, expert_offsets, blockscale_offsets,
         static_cast<uint8_t*>(quant_output), scale_factor, num_experts, k);
   }
   ES_CUDA_TRY(cudaGetLastError());
   return ES_B200_OK;
+}
+}  // namespace es_b200
+
+extern "C" int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, const int32_t* problem_sizes,
+                                           const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                           void* quant_output, uint8_t* scale_factor, int num_experts,
+                                           int64_t num_rows, int k, void* stream) {
+  return es_b200::quant_impl<false>(input, input_dtype, problem_sizes, expert_offsets, blockscale_offsets, quant_output,
+                                    scale_factor, num_experts, num_rows, k, stream);
+}
+
+extern "C" int es_b200_mxfp8_silu_mul_grouped_quant(const void* gate_up, int input_dtype, const int32_t* problem_sizes,
+                                                    const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                                    void* quant_output, uint8_t* scale_factor, int num_experts,
+                                                    int64_t num_rows, int k, void* stream) {
+  return es_b200::quant_impl<true>(gate_up, input_dtype, problem_sizes, expert_offsets, blockscale_offsets, quant_output,
+                                   scale_factor, num_experts, num_rows, k, stream);
 }

@@ -148,6 +148,7 @@ class ExpertShard:
         """x [rows_in, H] bf16 grouped by local expert -> [rows_in, H] bf16."""
         from .ops import es_sm100_mxfp8_blockscaled_grouped_mm as mm
         from .ops import es_sm100_mxfp8_blockscaled_grouped_quant as quant
+        from .ops import es_sm100_mxfp8_silu_mul_grouped_quant as silu_mul_quant
         rows = x.shape[0]
         dev = x.device
         ps1, eo, bo, sf_rows = plan.problem_tensors(self.n1, self.h)
@@ -156,11 +157,10 @@ class ExpertShard:
         quant(x, ps1, eo, bo, a, sfa)
         h1 = torch.empty((rows, self.n1), dtype=x.dtype, device=dev)
         mm(h1, a, self.w1.transpose(1, 2), sfa, self.sf1, ps1, eo, bo)
-        act = silu_mul(h1)
         ps2, _, _, _ = plan.problem_tensors(self.h, self.i)
         a2 = torch.empty((rows, self.i), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
         sfa2 = torch.empty((max(sf_rows, 128), self.i // 32), dtype=torch.uint8, device=dev)
-        quant(act, ps2, eo, bo, a2, sfa2)
+        silu_mul_quant(h1, ps2, eo, bo, a2, sfa2)      # fused SiLU * mul + requantisation, one pass over h1
         out = torch.empty((rows, self.h), dtype=x.dtype, device=dev)
         mm(out, a2, self.w2.transpose(1, 2), sfa2, self.sf2, ps2, eo, bo)
         return out

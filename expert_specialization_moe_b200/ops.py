@@ -13,6 +13,7 @@ __all__ = [
     "es_fp8_blockwise_scaled_grouped_mm",
     "es_sm100_mxfp8_blockscaled_grouped_mm",
     "es_sm100_mxfp8_blockscaled_grouped_quant",
+    "es_sm100_mxfp8_silu_mul_grouped_quant",
 ]
 
 
@@ -75,6 +76,35 @@ def es_sm100_mxfp8_blockscaled_grouped_quant(
         input.data_ptr(), dt, problem_sizes.data_ptr(), expert_offsets.data_ptr(), blockscale_offsets.data_ptr(),
         quant_output.data_ptr(), scale_factor.data_ptr(), groups, input.size(0), input.size(1),
         _stream_ptr(input)))
+
+
+def es_sm100_mxfp8_silu_mul_grouped_quant(
+    gate_up, problem_sizes, expert_offsets, blockscale_offsets, quant_output, scale_factor
+):
+    """Fused silu(gate) * up -> MXFP8 grouped quantisation; gate_up is [T, 2K] (gate | up), outputs as for
+    es_sm100_mxfp8_blockscaled_grouped_quant with K columns.  An addition of this library (the reference has no fused
+    ops): same bits as the unfused sequence, one pass over memory."""
+    _require_cuda(gate_up, problem_sizes, expert_offsets, blockscale_offsets, quant_output, scale_factor)
+    _check(gate_up.dim() == 2 and gate_up.size(1) % 256 == 0, "gate_up must be (rows, 2k) with k aligned to 128")
+    _check(gate_up.stride(1) == 1 and gate_up.stride(0) == gate_up.size(1), "gate_up must be densely packed row major")
+    k = gate_up.size(1) // 2
+    groups = problem_sizes.size(0)
+    _check(problem_sizes.dim() == 2 and problem_sizes.size(1) == 3 and problem_sizes.dtype == torch.int32
+           and problem_sizes.is_contiguous(), "problem_sizes must be a contiguous int32 tensor of shape (num_experts, 3)")
+    _check(expert_offsets.dim() == 1 and expert_offsets.size(0) == groups and expert_offsets.dtype == torch.int32
+           and expert_offsets.is_contiguous(), "expert_offsets must be contiguous int32 of length num_experts")
+    _check(blockscale_offsets.dim() == 1 and blockscale_offsets.size(0) == groups
+           and blockscale_offsets.dtype == torch.int32 and blockscale_offsets.is_contiguous(),
+           "blockscale_offsets must be contiguous int32 of length num_experts")
+    _check(quant_output.is_contiguous() and quant_output.numel() == gate_up.size(0) * k
+           and quant_output.element_size() == 1, "quant_output must be a contiguous 1-byte (rows, k) tensor")
+    _check(scale_factor.is_contiguous() and scale_factor.element_size() == 1,
+           "scale_factor must be a contiguous 1-byte tensor")
+    dt = _dtype_code(gate_up.dtype, "gate_up")
+    lib = _cabi.load()
+    _cabi.check(lib.es_b200_mxfp8_silu_mul_grouped_quant(
+        gate_up.data_ptr(), dt, problem_sizes.data_ptr(), expert_offsets.data_ptr(), blockscale_offsets.data_ptr(),
+        quant_output.data_ptr(), scale_factor.data_ptr(), groups, gate_up.size(0), k, _stream_ptr(gate_up)))
 
 
 def es_sm100_mxfp8_blockscaled_grouped_mm(

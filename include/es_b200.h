@@ -65,6 +65,19 @@ int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, const int32_
                                 void* stream);
 
 /*
+ * Fused SiLU * mul + MXFP8 grouped quantisation (between the gate_up and the down GEMM of an MoE layer).
+ * No counterpart in the reference, which has no fused ops; equivalent to computing
+ *   act = round_to_input_type( silu(gate_up[:, :k]) * gate_up[:, k:2k] )   (fp32 arithmetic, x / (1 + exp(-x)))
+ * and passing act to es_b200_mxfp8_grouped_quant — with the same result bits — but without writing and re-reading act.
+ *   gate_up [num_rows, 2k] bf16 or fp16, row-major: gate in columns [0,k), up in [k,2k); all other arguments and
+ *   the outputs (quant_output [num_rows, k], scale_factor) as for es_b200_mxfp8_grouped_quant.
+ */
+int es_b200_mxfp8_silu_mul_grouped_quant(const void* gate_up, int input_dtype, const int32_t* problem_sizes,
+                                         const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                         void* quant_output, uint8_t* scale_factor, int num_experts, int64_t num_rows,
+                                         int k, void* stream);
+
+/*
  * Scratch requirement (bytes, device memory, 256-byte aligned) of the two grouped GEMM entry points for a call
  * with these extents.  Stands where the reference allocates per-call torch::empty scratch tensors and a CUTLASS
  * workspace (es_sm100_mxfp8_blockscaled_launcher.cuh:163-176,140-142).  The kernels build their work lists in

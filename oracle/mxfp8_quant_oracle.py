@@ -152,6 +152,25 @@ def quantize_rows(x_bits: np.ndarray, is_bf16: bool, rcp448_bits: int = RCP_448_
     return codes, sf
 
 
+def silu_mul_bits(gate_up_bits: np.ndarray, is_bf16: bool) -> np.ndarray:
+    """[R, 2K] raw bits (gate | up) -> [R, K] raw bits of round_to_input_type(silu(gate) * up), fp32 arithmetic
+    x / (1 + exp(-x)).  (No reference counterpart: restates the unfused torch sequence silu(g.float()) * u.float().)
+    numpy's float32 exp can differ from the GPU's expf in the last bit, which rarely survives the rounding to 16 bits;
+    tests compare with a stated mismatch allowance and, exactly, with the unfused GPU sequence."""
+    R, K2 = gate_up_bits.shape
+    K = K2 // 2
+    conv = bf16_bits_to_f32 if is_bf16 else f16_bits_to_f32
+    g, u = conv(gate_up_bits[:, :K]), conv(gate_up_bits[:, K:])
+    with np.errstate(over="ignore", invalid="ignore"):
+        act = (g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))).astype(np.float32) * u
+    if is_bf16:
+        b = np.ascontiguousarray(act, dtype=np.float32).view(np.uint32)
+        nan = (b & np.uint32(0x7FFFFFFF)) > np.uint32(0x7F800000)
+        r = ((b + np.uint32(0x7FFF) + ((b >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+        return np.where(nan, np.uint16(0x7FFF), r).astype(np.uint16)
+    return act.astype(np.float16).view(np.uint16)
+
+
 # ----------------------------------------------------------------------------------------------
 # swizzled scale-factor layout (group_quant.cuh:25,294-310)
 # ----------------------------------------------------------------------------------------------

@@ -100,3 +100,45 @@ def test_quant_full_size_digest_matches_reference():
         assert hashlib.sha256(codes.tobytes()).hexdigest() == d["codes_sha256"]
         idx = C.valid_sf_index(counts, bo, K)
         assert hashlib.sha256(sf[idx].tobytes()).hexdigest() == d["sf_valid_sha256"]
+
+
+# ---- fused SiLU * mul + quant -----------------------------------------------------------------------------------
+def _run_silu_mul_quant(gu_bits, is_bf16, counts):
+    import torch
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_silu_mul_grouped_quant as fused
+    T, K2 = gu_bits.shape
+    K = K2 // 2
+    ps, eo, bo, sf_rows = Q.offsets_from_counts(counts, 0, K)
+    dev = "cuda"
+    gu = C.bits_to_tensor(gu_bits, is_bf16, dev)
+    codes = torch.zeros((T, K), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+    sf = torch.full((max(sf_rows, 1), K // 32), 0xCD, dtype=torch.uint8, device=dev)
+    fused(gu, torch.from_numpy(ps).to(dev), torch.from_numpy(eo).to(dev), torch.from_numpy(bo).to(dev), codes, sf)
+    torch.cuda.synchronize()
+    return codes.view(torch.uint8).cpu().numpy(), sf.cpu().numpy().reshape(-1)[: sf_rows * (K // 32)], gu
+
+
+@pytest.mark.parametrize("is_bf16", [True, False])
+@pytest.mark.parametrize("counts,K", [([5, 0, 130, 64], 128), ([300], 768), ([1] * 7 + [90], 2048)])
+def test_fused_silu_mul_quant_equals_unfused_sequence(counts, K, is_bf16):
+    """Bit-exact against the unfused GPU sequence (torch silu*mul in fp32 -> input type -> grouped quant op)."""
+    import torch
+    gu_bits = C.activations_bits(sum(counts), 2 * K, seed=K + len(counts), is_bf16=is_bf16, outliers=False)
+    codes, sf, gu = _run_silu_mul_quant(gu_bits, is_bf16, counts)
+    act = (torch.nn.functional.silu(gu[:, :K].float()) * gu[:, K:].float()).to(gu.dtype)
+    act_bits = act.view(torch.int16).cpu().numpy().view(np.uint16)
+    ucodes, usf, *_ = C.run_quant_op(act_bits, is_bf16, counts)
+    assert np.array_equal(codes, ucodes)
+    assert np.array_equal(sf, usf)
+
+
+def test_fused_silu_mul_quant_matches_cpu_oracle():
+    """Against the numpy oracle; its float32 exp may differ from the GPU's in the last bit, so a small fraction of
+    16-bit activations (and with them codes) may differ: allowance 1e-3 of the codes, scales 1e-3 of the bytes."""
+    counts, K = [40, 3, 200], 512
+    gu_bits = C.activations_bits(sum(counts), 2 * K, seed=5, outliers=False)
+    codes, sf, _ = _run_silu_mul_quant(gu_bits, True, counts)
+    act_bits = Q.silu_mul_bits(gu_bits, True)
+    ocodes, osf = C.oracle_quant(act_bits, True, counts)
+    assert (codes != ocodes).mean() < 1e-3
+    assert (sf != osf).mean() < 1e-3
