@@ -85,6 +85,23 @@ def algorithmic_bytes(counts, N, K):
     return T * K + T * K // 32 + active * N * K + active * N * K // 32 + 2 * T * N
 
 
+def shard_counts(counts_all, world, placement):
+    """Row counts of the experts each rank owns.  contiguous: experts [r*E/G, (r+1)*E/G).  balanced: experts sorted by
+    rows, each assigned to the least-loaded rank that still has room (E/G experts per rank) — the static placement an
+    expert-parallel deployment would derive from load statistics."""
+    E = len(counts_all)
+    per = E // world
+    if placement == "contiguous" or world == 1:
+        return [counts_all[r * per:(r + 1) * per] for r in range(world)]
+    order = np.argsort(-counts_all, kind="stable")
+    load = [0] * world
+    owned = [[] for _ in range(world)]
+    for e in order:
+        r = min((i for i in range(world) if len(owned[i]) < per), key=lambda i: load[i])
+        owned[r].append(int(e)); load[r] += int(counts_all[e])
+    return [counts_all[np.array(sorted(o))] for o in owned]
+
+
 def peak_hbm():
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
@@ -298,6 +315,9 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=20.0, help="seconds of CPU work for the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--placement", default="contiguous", choices=["contiguous", "balanced"],
+                    help="expert-to-GPU placement for N > 1: contiguous blocks of E/N experts, or E/N experts per GPU "
+                         "chosen greedily (largest first) so that routed rows are balanced")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -350,10 +370,10 @@ def main():
     if args.workload.startswith("quant"):
         return bench_quant(args, E, T, K, desc, device, rank, world, dist)
 
-    # expert-parallel shard: contiguous E/world experts per rank
+    # expert-parallel shard: E/world experts per rank
     assert E % world == 0
-    e_lo, e_hi = rank * (E // world), (rank + 1) * (E // world)
-    counts = counts_all[e_lo:e_hi]
+    counts = shard_counts(counts_all, world, args.placement)[rank]
+    config["placement"] = args.placement
     wl = build_device_workload(counts, N, K, device, seed=1000 + rank)
     from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_mm as grouped_mm
     from expert_specialization_moe_b200 import _cabi
