@@ -47,6 +47,7 @@ WORKLOADS = {
     # grouped MXFP8 quantisation alone (N is unused): bf16 N(0,1) with 1% outliers x50
     "quant": (256, 32768, 0, 7168, "grouped MXFP8 quantisation: bf16 [32768, 7168], E=256, Zipf(1.2) counts, "
                                    "e4m3 codes + swizzled UE8M0 scales"),
+    "qwen3_ep": (128, 0, 0, 0, "Qwen3-30B-A3B-shaped MoE layer with expert parallelism (N >= 2)"),
     "quant_small": (64, 8192, 0, 7168, "grouped MXFP8 quantisation at 1/4 scale for profiler captures: bf16 "
                                        "[8192, 7168], E=64"),
 }
@@ -245,6 +246,62 @@ def cpu_reference_rate(counts, N, K, seed, budget_s=20.0, threads=None):
     return rate, threads, desc
 
 
+def bench_ep_layer(args, device, rank, world, dist):
+    """Qwen3-30B-A3B-shaped MoE layer, expert parallel: E=128, top-8, hidden 2048, moe_intermediate 768, 16384 tokens
+    per GPU, router logits N(0,1) -> softmax -> top-8.  One step = count exchange + NCCL all-to-all dispatch + grouped
+    quant + gate_up grouped GEMM + fused SiLU*mul/requant + down grouped GEMM + all-to-all combine with top-k weights
+    (expert_parallel.moe_forward).  Needs N >= 2 ranks; value = expert-GEMM FLOPs of all ranks / step time."""
+    from expert_specialization_moe_b200 import expert_parallel as ep
+    E, topk, H, I, tokens = 128, 8, 2048, 768, 16384
+    assert dist is not None and E % world == 0, "the expert-parallel layer benchmark needs 2, 4 or 8 ranks"
+    e_local = E // world
+    g = torch.Generator(device=device); g.manual_seed(1234)           # same weights everywhere; each rank keeps a shard
+    w1 = (torch.randn((E, 2 * I, H), generator=g, device=device) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn((E, H, I), generator=g, device=device) * 0.02).to(torch.bfloat16)
+    shard = ep.ExpertShard(w1[rank * e_local:(rank + 1) * e_local].contiguous(),
+                           w2[rank * e_local:(rank + 1) * e_local].contiguous())
+    del w1, w2
+    g.manual_seed(99 + rank)
+    x = torch.randn((tokens, H), generator=g, device=device).to(torch.bfloat16)
+    p = torch.softmax(torch.randn((tokens, E), generator=g, device=device), -1)
+    wts, ids = torch.topk(p, topk, dim=-1)
+    wts = (wts / wts.sum(-1, keepdim=True)).to(torch.float32)
+    step = lambda: ep.moe_forward(x, ids, wts, E, shard.forward)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(device.index or 0)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=device)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        flops = 2.0 * tokens * topk * world * (2 * I * H + H * I)
+        line = {"metric": "MoE layer (expert parallel) grouped-GEMM TFLOPS incl. dispatch/combine",
+                "value": flops / (float(ms[0]) * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": float(ms[0]), "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "mxfp8_e4m3", "data": "synthetic",
+                "config": {"workload": "Qwen3-30B-A3B-shaped MoE layer: E=128, top-8, hidden 2048, intermediate 768, "
+                                       "16384 tokens per GPU, NCCL all-to-all dispatch/combine", "experts_per_gpu": e_local},
+                "clocks": clocks, "gpu_launches": args.steps * 7}
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def bench_quant(args, E, T, K, desc, device, rank, world, dist):
     """Grouped quant alone; with N GPUs each rank quantises its own E/N experts' rows (no collective)."""
     from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
@@ -369,6 +426,8 @@ def main():
 
     if args.workload.startswith("quant"):
         return bench_quant(args, E, T, K, desc, device, rank, world, dist)
+    if args.workload == "qwen3_ep":
+        return bench_ep_layer(args, device, rank, world, dist)
 
     # expert-parallel shard: E/world experts per rank
     assert E % world == 0

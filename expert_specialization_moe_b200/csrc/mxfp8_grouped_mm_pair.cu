@@ -49,6 +49,7 @@ constexpr uint32_t SF_SLOT_COLS = 16;
 static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 
 constexpr uint32_t ERR_PRODUCER = 0x10u, ERR_MMA = 0x20u, ERR_EPILOGUE = 0x40u;
+constexpr uint32_t ERR_SCALE_OFFSET = 0x80u;   // a blockscale offset that is not a multiple of 128 rows
 
 struct SharedCtl {
   uint64_t full[STAGES];        // used in the leader CTA only
@@ -216,7 +217,9 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       const int w_row = ti.e * n + nt * TILE_N;             // may run past the expert when n/128 is odd: not stored
       if (nt >= n_tiles) nt = n_tiles - 1;                  // keep the scale-atom load inside the buffer
       const int sfw_atom = ti.e * sfw_atoms_per_expert + nt * kt_count;
-      const int sfx_atom = ((blockscale_offsets[ti.e] >> 7) + ti.atom0) * kt_count;
+      const int bs_off = blockscale_offsets[ti.e];
+      if ((bs_off & 127) != 0 && lane == 0) atomicOr(&g_status, ERR_SCALE_OFFSET);   // reported by es_b200_check_status
+      const int sfx_atom = ((bs_off >> 7) + ti.atom0) * kt_count;
       // this lane's load: 0 weights, 1 tokens of sub-tile 0, 2 tokens of sub-tile 1, 3 weight scales,
       // 4..6 token scale atoms
       const bool active = lane == 0 || lane == 1 || (lane == 2 && ti.n1 > 0) || lane == 3 ||

@@ -95,7 +95,8 @@ size_t es_b200_grouped_mm_scratch_bytes(int num_experts, int64_t num_rows, int n
  *   a    [num_rows, k] e4m3, row-major                      b   [num_experts, n, k] e4m3 in memory (the reference's
  *   sfa  swizzled UE8M0, expert e at blockscale_offsets[e]*k/32     [E, k, n] view with stride(1) == 1)
  *   sfb  swizzled UE8M0, expert e at e*n*k/32                d   [num_rows, n] bf16 or fp16
- *   k % 128 == 0, n % 128 == 0; a, b, d 16-byte aligned; sfa, sfb 16-byte aligned.
+ *   k % 128 == 0, n % 128 == 0; a, b, d 16-byte aligned; sfa, sfb 16-byte aligned; blockscale_offsets multiples of
+ *   128 (they are cumulative round-ups of the row counts to 128, as the reference's callers build them).
  * fp32 accumulation on the tensor cores, round-to-nearest to the output type.  Rows outside every expert's range
  * are not written.
  */
