@@ -203,47 +203,60 @@ def build_device_workload(counts, N, K, device, seed):
                 ps_h=ps, eo_h=eo, bo_h=bo)
 
 
-def cpu_reference_rate(counts, N, K, seed, budget_s=20.0, threads=None):
-    """Times the CPU path (dequantise + per-expert fp32 torch.mm, oracle/grouped_gemm_oracle.py — the restatement of
-    the reference's torch dequant-matmul path) on a bounded sample: experts are taken in index order until the time
-    budget is used.  Returns (TFLOP/s, cores, description)."""
-    from oracle import grouped_gemm_oracle as G
-    from oracle import mxfp8_quant_oracle as Q
-    threads = threads or os.cpu_count() or 1
-    torch.set_num_threads(threads)
-    rng = np.random.default_rng(seed)
-    flops, secs, used = 0.0, 0.0, []
+class CpuReferenceSample:
+    """Bounded sample of the workload for the CPU path (dequantise + per-expert fp32 torch.mm,
+    oracle/grouped_gemm_oracle.py — the restatement of the reference's torch dequant-matmul path).  Operands are built
+    once; run() times one pass over the sample on all host threads."""
 
-    def random_mxfp8(rows):
-        # operand bytes drawn directly (finite e4m3 codes of either sign, scale exponents around 2^-7): the CPU time
-        # of dequantise + matmul does not depend on the values, and quantising 29 M weights per expert with the numpy
-        # oracle would dominate the wall clock of this leg
-        codes = rng.integers(0, 0x7F, size=(rows, K), dtype=np.uint8) | (rng.integers(0, 2, size=(rows, K), dtype=np.uint8) << 7)
-        sf = rng.integers(118, 123, size=(rows, K // 32), dtype=np.uint8)
-        return codes, torch.from_numpy(Q.swizzle_sf(sf, K))
+    def __init__(self, counts, N, K, seed, max_flops):
+        from oracle import mxfp8_quant_oracle as Q
+        rng = np.random.default_rng(seed)
+        self.N, self.K = N, K
 
-    wc, sfb = random_mxfp8(N)
-    w_t = torch.from_numpy(wc).view(1, N, K)
-    for e in range(len(counts)):
-        m = int(counts[e])
-        if m == 0:
-            continue
-        ac, sfa = random_mxfp8(m)
-        ps = np.array([[m, N, K]], dtype=np.int32)
-        a_t = torch.from_numpy(ac)
+        def random_mxfp8(rows):
+            # operand bytes drawn directly (finite e4m3 codes of either sign, scale exponents around 2^-7): the CPU
+            # time of dequantise + matmul does not depend on the values, and quantising 29 M weights per expert with
+            # the numpy oracle would dominate the wall clock of this leg
+            codes = rng.integers(0, 0x7F, size=(rows, K), dtype=np.uint8) | (rng.integers(0, 2, size=(rows, K), dtype=np.uint8) << 7)
+            sf = rng.integers(118, 123, size=(rows, K // 32), dtype=np.uint8)
+            return torch.from_numpy(codes), torch.from_numpy(Q.swizzle_sf(sf, K))
+
+        self.w, self.sfb = random_mxfp8(N)
+        self.w = self.w.view(1, N, K)
+        self.items, self.flops, self.rows, self.experts = [], 0.0, 0, []
+        for e in range(len(counts)):
+            m = int(counts[e])
+            if m == 0:
+                continue
+            a, sfa = random_mxfp8(m)
+            self.items.append((a, sfa, np.array([[m, N, K]], dtype=np.int32)))
+            self.flops += 2.0 * m * N * K
+            self.rows += m
+            self.experts.append(e)
+            if self.flops >= max_flops:
+                break
+
+    def run(self, threads=None):
+        from oracle import grouped_gemm_oracle as G
+        threads = threads or os.cpu_count() or 1
+        torch.set_num_threads(threads)
         t0 = time.perf_counter()
-        G.mxfp8_grouped_mm(a_t, w_t, sfa, sfb, ps, [0], [0])
-        dt = time.perf_counter() - t0
-        secs += dt
-        flops += 2.0 * m * N * K
-        used.append(e)
-        if secs >= budget_s:
-            break
-    rate = flops / secs / 1e12 if secs > 0 else 0.0
-    rows = int(sum(int(counts[e]) for e in used))
-    desc = (f"experts {used[0]}..{used[-1]} of the workload ({len(used)} non-empty experts, {rows} rows, "
-            f"{flops / 1e9:.1f} GFLOP) in {secs:.1f} s: unswizzle + dequantise + fp32 torch.mm per expert")
-    return rate, threads, desc
+        for a, sfa, ps in self.items:
+            G.mxfp8_grouped_mm(a, self.w, sfa, self.sfb, ps, [0], [0])
+        secs = time.perf_counter() - t0
+        return self.flops / secs / 1e12, threads, secs
+
+    def describe(self, secs):
+        return (f"experts {self.experts[0]}..{self.experts[-1]} of the workload ({len(self.experts)} non-empty experts, "
+                f"{self.rows} rows, {self.flops / 1e9:.1f} GFLOP) in {secs:.1f} s: unswizzle + dequantise + fp32 "
+                f"torch.mm per expert")
+
+
+def cpu_reference_rate(counts, N, K, seed, budget_s=20.0, threads=None):
+    """One timed pass over a sample sized for about `budget_s` seconds (assuming ~0.2 TFLOP/s of host throughput)."""
+    sample = CpuReferenceSample(counts, N, K, seed, max_flops=budget_s * 0.2e12)
+    rate, threads, secs = sample.run(threads)
+    return rate, threads, sample.describe(secs)
 
 
 def bench_ep_layer(args, device, rank, world, dist):
@@ -394,11 +407,16 @@ def main():
             return
         rates = []
         cores = os.cpu_count() or 1
-        per_step_budget = max(2.0, min(args.cpu_budget, 120.0 / max(1, args.steps + args.warmup)))
+        # the whole run (warm-up + steps) is kept to about two minutes: each step times one pass over a sample sized
+        # for total / (steps + warm-up) seconds at ~0.2 TFLOP/s
+        per_step_budget = min(args.cpu_budget, max(0.25, 100.0 / max(1, args.steps + args.warmup)))
+        sample = CpuReferenceSample(counts_all, N, K, seed=100, max_flops=per_step_budget * 0.2e12)
+        sdesc = ""
         for i in range(args.warmup + args.steps):
-            r, cores, sdesc = cpu_reference_rate(counts_all, N, K, seed=100 + i, budget_s=per_step_budget)
+            r, cores, secs = sample.run()
             if i >= args.warmup:
                 rates.append(r)
+                sdesc = sample.describe(secs)
         v = float(np.mean(rates)) if rates else 0.0
         flops_total = 2.0 * T * N * K
         line = {

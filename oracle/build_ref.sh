@@ -6,7 +6,7 @@
 # usage: oracle/build_ref.sh <path-to-reference-checkout>
 # Needs: nvcc 12.9, the CUTLASS 4.x header tree bundled with flashinfer, torch headers.
 set -euo pipefail
-REF=${1:-/root/reference}
+REF=${1:?usage: oracle/build_ref.sh <path-to-reference-checkout>}
 HERE=$(cd "$(dirname "$0")" && pwd)
 OUT=$HERE/_ref
 mkdir -p "$OUT"

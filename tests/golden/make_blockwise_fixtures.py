@@ -1,6 +1,6 @@
 """Generate tests/golden/ref_blockwise_*.npz by running the REFERENCE's own torch code on the CPU.
 
-    python tests/golden/make_blockwise_fixtures.py [/path/to/reference]
+    python tests/golden/make_blockwise_fixtures.py /path/to/reference
 
 The reference's test module (test/test_es_grouped_gemm.py) defines the quantisers per_token_cast_to_fp8 /
 per_block_cast_to_fp8 and the dequantise-and-matmul path baseline_scaled_mm.  The module imports the compiled
@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else HERE.parent.parent.parent / "reference"   # a sibling checkout
 
 
 def load_reference_test_module():
