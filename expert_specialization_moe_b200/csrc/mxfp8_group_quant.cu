@@ -26,7 +26,7 @@ constexpr int QUANT_UNROLL = 4;                             // 16-byte loads in 
 
 __device__ __forceinline__ float rcp_approx_ftz(float a) {
   float b;
-  asm volatile("rcp.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(a));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(b) : "f"(a));   // pure: may be hoisted / scheduled freely
   return b;
 }
 
