@@ -25,7 +25,8 @@ __device__ __forceinline__ __half out_from_f32<__half>(float v) { return __float
 // Drains `n_cols` accumulator columns (a multiple of 16) starting at TMEM address `taddr` (this warp's lane quadrant)
 // and stores the first `valid` of them: column j goes to dst[j * ld + 0..31] (dst = &d[first token][first n of warp]).
 // `release` is called once, right after the last TMEM read has completed (the accumulator may then be overwritten).
-template <typename OutT, class Release>
+// TOK = tokens per pass through the shared-memory tile (32: 2 KB per warp; 16: 1 KB per warp, two passes per chunk).
+template <typename OutT, int TOK = 32, class Release>
 __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, int valid, OutT* stage_warp, OutT* dst,
                                                   int64_t ld, bool do_store, int lane, Release release) {
   // two register sets: the TMEM read of chunk c+1 is in flight while chunk c goes through shared memory
@@ -46,16 +47,20 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
       }
       if (do_store) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          stage_warp[j * 32 + lane] = out_from_f32<OutT>(__uint_as_float(h == 0 ? va[j] : vb[j]));
-        __syncwarp();
+        for (int p = 0; p < 32 / TOK; ++p) {
 #pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int tok = it * 8 + (lane >> 2);
-          const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
-          if (c + tok < valid) *reinterpret_cast<uint4*>(dst + (int64_t)(c + tok) * ld + part * 8) = val;
+          for (int j = 0; j < TOK; ++j)
+            stage_warp[j * 32 + lane] = out_from_f32<OutT>(__uint_as_float(h == 0 ? va[p * TOK + j] : vb[p * TOK + j]));
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < TOK / 8; ++it) {
+            const int tok = it * 8 + (lane >> 2);
+            const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
+            const int row = c + p * TOK + tok;
+            if (row < valid) *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
+          }
+          __syncwarp();
         }
-        __syncwarp();
       }
     }
   }

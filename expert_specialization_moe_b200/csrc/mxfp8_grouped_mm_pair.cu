@@ -15,10 +15,18 @@
 //   warp 0    producer (both CTAs): per K step lanes 0..6 each issue one TMA load (own weight rows, own halves of
 //             the two token sub-tiles, own weight scale atom, the item's token scale atoms); all completion bytes
 //             are credited to the leader CTA's barrier
-//   warp 1    TMEM allocation (both CTAs); in the leader CTA one lane issues tcgen05.cp (scales smem -> TMEM of
-//             both CTAs) and 4 + 4 tcgen05.mma per K step, and commits to the barriers of both CTAs
-//   warps 2-5 epilogue (both CTAs): own 128 accumulator lanes -> bf16/fp16 -> global, sub-tile 0 then sub-tile 1,
-//             so that the next item's first MMAs can start while the second accumulator is still being drained
+//   warp 1    TMEM allocation (both CTAs); in the leader CTA one lane issues sub-tile 0's four tcgen05.mma per K step
+//   warps 2-5 epilogue of accumulator 0 (both CTAs): own 128 accumulator lanes -> bf16/fp16 -> global
+//   warps 6-9 epilogue of accumulator 1, at the same time as warps 2-5
+//   warp 10   leader CTA, one lane: sub-tile 1's four tcgen05.mma per K step
+//   warp 11   leader CTA, one lane: the K step's four tcgen05.cp (scales smem -> TMEM of both CTAs)
+//
+// Three issuing lanes instead of one because a tcgen05 instruction costs the thread that issues it ~90 cycles (mma)
+// or ~65 cycles (cp) whatever its size (measured: the K step of a single issuing lane took the same ~1000 cycles with
+// N = 64 and with N = 256 MMAs), while the tensor pipe needs 96 cycles for a 256 x 192 x 32 MMA.  One lane issuing
+// 8 MMAs + 4 copies + a commit per K step is therefore issue-bound at ~1260 cycles for 768 cycles of tensor work;
+// split three ways every lane stays below the pipe's time.  The lanes meet only through mbarriers: the copy lane
+// commits to sf_ready[stage], both MMA lanes commit to empty[stage] (2 arrivals) and to their accumulator's barrier.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -30,7 +38,7 @@
 namespace es_b200 {
 namespace mm2 {
 
-constexpr int THREADS = 192;
+constexpr int THREADS = 384;
 constexpr int TILE_N = 128;      // weight rows per CTA (the pair covers 256)
 constexpr int TILE_K = 128;
 constexpr int SUB_TILE = 192;    // token rows per accumulator (MMA N, runtime multiple of 16)
@@ -50,10 +58,15 @@ static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 
 constexpr uint32_t ERR_PRODUCER = 0x10u, ERR_MMA = 0x20u, ERR_EPILOGUE = 0x40u;
 constexpr uint32_t ERR_SCALE_OFFSET = 0x80u;   // a blockscale offset that is not a multiple of 128 rows
+constexpr uint32_t ERR_SCALE_COPY = 0x100u;
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_TOK = 16;                                // tokens per pass of an epilogue warp's shared-memory tile
+constexpr int EPI_BYTES_PER_WARP = EPI_TOK * 32 * 2;       // 1 KB
 
 struct SharedCtl {
   uint64_t full[STAGES];        // used in the leader CTA only
-  uint64_t empty[STAGES];
+  uint64_t empty[STAGES];       // 2 arrivals: one commit from each MMA lane
+  uint64_t sf_ready[STAGES];    // leader only: the stage's scales are in the TMEM of both CTAs
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];       // used in the leader CTA only (8 arrivals: 4 epilogue warps x 2 CTAs)
                                 // index = accumulator (sub-tile 0 / 1)
@@ -67,7 +80,8 @@ struct SharedCtl {
 #endif
 };
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + sizeof(SharedCtl);
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + EPI_WARPS * EPI_BYTES_PER_WARP + sizeof(SharedCtl);
+static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA per SM");
 
 __device__ uint32_t g_status = 0;
 #ifdef ES_PROFILE
@@ -140,8 +154,8 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
                              int wait_at_start) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 4 x 2 KB, one per epilogue warp
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + 4 * EPI_STAGE_BYTES_PER_WARP);
+  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 8 x 1 KB, one per epilogue warp
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + EPI_WARPS * EPI_BYTES_PER_WARP);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
@@ -151,7 +165,8 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       ptx::mbar_init(&ctl->full[s], 1);
-      ptx::mbar_init(&ctl->empty[s], 1);
+      ptx::mbar_init(&ctl->empty[s], 2);
+      ptx::mbar_init(&ctl->sf_ready[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&ctl->tmem_full[a], 1);
@@ -265,66 +280,51 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       atomicAdd(&g_prof[2 + 4 * rank], (unsigned long long)_acc[2]);
     }
 #endif
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issue (leader CTA, one lane)
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issue (leader CTA): warp 1 issues the
+    // MMAs of sub-tile 0 into accumulator 0, warp 10 those of sub-tile 1 into accumulator 1
     if (lane == 0 && rank == 0) {
+      const int sub = warp == 1 ? 0 : 1;
       int s = 0;
       uint32_t ph = 0;
-      uint32_t acc_ph[2] = {0, 0};     // phase of each accumulator's empty barrier (advances once per use)
+      uint32_t acc_ph = 0;             // phase of this accumulator's empty barrier (advances once per use)
       bool ok = true;
 #ifdef ES_PROFILE
       long long _acc[4] = {0, 0, 0, 0};
+      const long long _c0 = clock64();
+      const unsigned long long _g0 = ptx::globaltimer_ns();
 #endif
       PROF_T0();
       for (int t = pair; ok && t < total_tiles; t += num_pairs) {
         const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-        const uint32_t d0 = tmem_base, d1 = tmem_base + ACC_COLS;
+        const uint32_t n_mma = sub == 0 ? ti.n0 : ti.n1;
+        const uint32_t d_acc = tmem_base + sub * ACC_COLS;
         for (int kt = 0; ok && kt < kt_count; ++kt) {
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
           PROF_ADD(1);
-#ifdef ES_PROFILE
-          _acc[3] += clock64() - ctl->t_issue[s];
-#endif
-          ptx::tc_fence_after_sync();
-          const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
-          const uint32_t sfw_t = tmem_base + SF_COL0 + s * SF_SLOT_COLS;
-          const uint32_t sfx_t = sfw_t + 4;
-          const uint32_t sf_smem = stage + W_BYTES + 2 * X_BYTES;
-          // scale copies: sub-tile 0 (rows 0..191) needs token atoms 0 and 1, sub-tile 1 (rows 192..383) atoms 1
-          // and 2; the third atom's copy is issued behind sub-tile 0's MMAs, which do not depend on it
-          ptx::tc_cp_sf_pair(sfw_t, ptx::make_desc_sf(sf_smem));
-          ptx::tc_cp_sf_pair(sfx_t, ptx::make_desc_sf(sf_smem + SFW_BYTES));
-          if (ti.n_atoms > 1) ptx::tc_cp_sf_pair(sfx_t + 4, ptx::make_desc_sf(sf_smem + SFW_BYTES + 512));
-          const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
-          const uint64_t b0_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
-          const uint64_t b1_desc = ptx::make_desc_k_sw128(stage + W_BYTES + X_BYTES);
-          if (kt == 0) {   // the previous item's epilogue must have drained accumulator 0
-            if (!ptx::mbar_wait(&ctl->tmem_empty[0], acc_ph[0] ^ 1u, abort_flag)) { ok = false; break; }
-            acc_ph[0] ^= 1u;
-            ptx::tc_fence_after_sync();
-            PROF_ADD(0);
-          }
-#pragma unroll
-          for (uint32_t j = 0; j < 4; ++j)
-            ptx::tc_mma_mxf8_pair(d0, a_desc + 2 * j, b0_desc + 2 * j, ptx::make_idesc_mxf8(2 * TILE_N, ti.n0, j, j),
-                                  sfw_t | (j << 30), sfx_t | (j << 30), (kt | j) != 0 ? 1u : 0u);
-          if (ti.n1 > 0) {
-            if (ti.n_atoms > 2) ptx::tc_cp_sf_pair(sfx_t + 8, ptx::make_desc_sf(sf_smem + SFW_BYTES + 1024));
-            if (kt == 0) {
-              if (!ptx::mbar_wait(&ctl->tmem_empty[1], acc_ph[1] ^ 1u, abort_flag)) { ok = false; break; }
-              acc_ph[1] ^= 1u;
-              ptx::tc_fence_after_sync();
+          if (n_mma > 0) {
+            if (!ptx::mbar_wait(&ctl->sf_ready[s], ph, abort_flag)) { ok = false; break; }
+            PROF_ADD(3);
+            if (kt == 0) {   // the previous item's epilogue must have drained this accumulator
+              if (!ptx::mbar_wait(&ctl->tmem_empty[sub], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
+              acc_ph ^= 1u;
               PROF_ADD(0);
             }
-            // sub-tile 1 starts 192 rows = 6 scale columns into the item's scale block
+            ptx::tc_fence_after_sync();
+            const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
+            const uint32_t sfw_t = tmem_base + SF_COL0 + s * SF_SLOT_COLS;
+            // sub-tile 1 starts 192 rows = 6 scale columns into the item's block of token scales
+            const uint32_t sfx_t = sfw_t + 4 + sub * 6;
+            const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
+            const uint64_t b_desc = ptx::make_desc_k_sw128(stage + W_BYTES + sub * X_BYTES);
 #pragma unroll
             for (uint32_t j = 0; j < 4; ++j)
-              ptx::tc_mma_mxf8_pair(d1, a_desc + 2 * j, b1_desc + 2 * j, ptx::make_idesc_mxf8(2 * TILE_N, ti.n1, j, j),
-                                    sfw_t | (j << 30), (sfx_t + 6) | (j << 30), (kt | j) != 0 ? 1u : 0u);
+              ptx::tc_mma_mxf8_pair(d_acc, a_desc + 2 * j, b_desc + 2 * j, ptx::make_idesc_mxf8(2 * TILE_N, n_mma, j, j),
+                                    sfw_t | (j << 30), sfx_t | (j << 30), (kt | j) != 0 ? 1u : 0u);
           }
-          ptx::tc_commit_pair(&ctl->empty[s], 3);       // both CTAs may refill the stage
+          ptx::tc_commit_pair(&ctl->empty[s], 3);       // this lane's share: both CTAs may refill once both have
 #ifdef ES_PROFILE
-          ctl->t_commit[s] = clock64();
+          if (sub == 0) ctl->t_commit[s] = clock64();
 #endif
           if (++s == STAGES) { s = 0; ph ^= 1u; }
           PROF_ADD(2);
@@ -334,49 +334,76 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
           atomicOr(&g_status, ERR_MMA);
           break;
         }
-        ptx::tc_commit_pair(&ctl->tmem_full[0], 3);     // accumulators of both CTAs complete
-        if (ti.n1 > 0) ptx::tc_commit_pair(&ctl->tmem_full[1], 3);
+        if (n_mma > 0) ptx::tc_commit_pair(&ctl->tmem_full[sub], 3);     // this accumulator is complete in both CTAs
       }
 #ifdef ES_PROFILE
-      atomicAdd(&g_prof[8], (unsigned long long)_acc[0]);
-      atomicAdd(&g_prof[9], (unsigned long long)_acc[1]);
-      atomicAdd(&g_prof[10], (unsigned long long)_acc[2]);
-      atomicAdd(&g_prof[11], 1ull);
-      atomicAdd(&g_prof[12], (unsigned long long)_acc[3]);
+      atomicAdd(&g_prof[sub == 0 ? 8 : 13], (unsigned long long)_acc[0]);
+      atomicAdd(&g_prof[sub == 0 ? 9 : 14], (unsigned long long)_acc[1]);
+      atomicAdd(&g_prof[sub == 0 ? 10 : 15], (unsigned long long)_acc[2]);
+      if (sub == 0) atomicAdd(&g_prof[11], 1ull);
+      if (sub == 0) atomicAdd(&g_prof[3], (unsigned long long)(clock64() - _c0));
+      if (sub == 0) atomicAdd(&g_prof[7], (unsigned long long)(ptx::globaltimer_ns() - _g0));
+      if (sub == 0) atomicAdd(&g_prof[12], (unsigned long long)_acc[3]);
 #endif
     }
+  } else if (warp == 11) {
+    // ------------------------------------------------------------------ scale copies (leader CTA, one lane)
+    // Token rows 0..383 of the item = scale atoms 0..2: sub-tile 0 reads atoms 0 and 1, sub-tile 1 atoms 1 and 2.
+    if (lane == 0 && rank == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = pair; ok && t < total_tiles; t += num_pairs) {
+        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        for (int kt = 0; kt < kt_count; ++kt) {
+          if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t sf_smem = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES) + W_BYTES + 2 * X_BYTES;
+          const uint32_t sfw_t = tmem_base + SF_COL0 + s * SF_SLOT_COLS;
+          ptx::tc_cp_sf_pair(sfw_t, ptx::make_desc_sf(sf_smem));
+          ptx::tc_cp_sf_pair(sfw_t + 4, ptx::make_desc_sf(sf_smem + SFW_BYTES));
+          if (ti.n_atoms > 1) ptx::tc_cp_sf_pair(sfw_t + 8, ptx::make_desc_sf(sf_smem + SFW_BYTES + 512));
+          if (ti.n_atoms > 2) ptx::tc_cp_sf_pair(sfw_t + 12, ptx::make_desc_sf(sf_smem + SFW_BYTES + 1024));
+          ptx::tc_commit_pair(&ctl->sf_ready[s], 1);    // leader's barrier, once the copies have landed in both TMEMs
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_SCALE_COPY);
+        }
+      }
+    }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+    // ------------------------------------------------------------------ epilogue (both CTAs): warps 2..5 drain
+    // accumulator 0, warps 6..9 accumulator 1, at the same time
     const int q = warp & 3;
-    uint32_t full_ph[2] = {0, 0};
-    bool alive = true;
-    for (int t = pair; alive && t < total_tiles; t += num_pairs) {
+    const int sub = (warp - 2) >> 2;
+    uint32_t full_ph = 0;
+    for (int t = pair; t < total_tiles; t += num_pairs) {
       const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      if (sub == 1 && ti.n1 == 0) continue;               // an item of <= 192 rows does not use accumulator 1
       const int nt = ti.np * 2 + (int)rank;
       const bool store = nt < n_tiles;
-      for (int sub = 0; sub < (ti.n1 > 0 ? 2 : 1); ++sub) {
-        const int n_mma = sub == 0 ? ti.n0 : ti.n1;
-        const int valid = sub == 0 ? ti.v0 : ti.v1;
-        const bool got = ptx::mbar_wait(&ctl->tmem_full[sub], full_ph[sub], abort_flag);
-        if (!__all_sync(0xffffffffu, got)) {
-          if (lane == 0) {
-            *abort_flag = 1;
-            atomicOr(&g_status, ERR_EPILOGUE);
-          }
-          alive = false;
-          break;
+      const int n_mma = sub == 0 ? ti.n0 : ti.n1;
+      const int valid = sub == 0 ? ti.v0 : ti.v1;
+      const bool got = ptx::mbar_wait(&ctl->tmem_full[sub], full_ph, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_EPILOGUE);
         }
-        full_ph[sub] ^= 1u;
-        ptx::tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + sub * ACC_COLS + ((uint32_t)(q * 32) << 16);
-        OutT* dst = d + (int64_t)(ti.row0 + sub * SUB_TILE) * n + (nt * TILE_N + q * 32);
-        drain_accumulator<OutT>(taddr, n_mma, valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, dst, n,
-                                store, lane, [&] {
-                                  ptx::tc_fence_before_sync();
-                                  __syncwarp();
-                                  if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[sub], 0);   // leader's barrier
-                                });
+        break;
       }
+      full_ph ^= 1u;
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + sub * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      OutT* dst = d + (int64_t)(ti.row0 + sub * SUB_TILE) * n + (nt * TILE_N + q * 32);
+      drain_accumulator<OutT, EPI_TOK>(taddr, n_mma, valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * (EPI_TOK * 32),
+                                       dst, n, store, lane, [&] {
+                                         ptx::tc_fence_before_sync();
+                                         __syncwarp();
+                                         if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[sub], 0);   // leader's barrier
+                                       });
     }
   }
 
