@@ -3,49 +3,95 @@
 // Per expert e:  d[off_e + i, n] = sum_kb sa[off_e + i, kb] * sb[e, n/128, kb] * sum_{k in kb} a[off_e + i, k] * b[e, n, k]
 //
 // The reference runs this op on Hopper only (wgmma templates).  Here every 128-wide K block is one unscaled
-// tcgen05.mma.kind::f8f6f4 group (4 MMAs of K=32) into a TMEM partial buffer; the four epilogue warps pull each
-// partial out of TMEM (tcgen05.ld), multiply by the block's scale product and accumulate in fp32 registers, while
-// the tensor core already works on the next K block in the second partial buffer (two-stage promotion).
-// Same mapping as the MXFP8 kernels: 128 weight rows on the MMA M axis, the expert's tokens on the runtime-sized
-// MMA N axis (multiple of 16, <= 128), work list from a per-CTA prefix scan, persistent grid of one CTA per SM.
+// tcgen05.mma.kind::f8f6f4 group (4 MMAs of K=32) into one of FOUR TMEM partial buffers; the epilogue warps pull
+// each partial out of TMEM (tcgen05.ld), multiply by the block's scale product and accumulate in fp32 registers
+// while the tensor core works up to three K blocks ahead (two-stage promotion, as the reference's Hopper kernel
+// does in registers).  Same mapping as the MXFP8 kernels: 128 weight rows on the MMA M axis, the expert's tokens on
+// the runtime-sized MMA N axis (multiple of 16), work list from a per-CTA prefix scan, persistent grid of one CTA
+// per SM, one launch per row-count bucket (<= 32, 33..64, >= 65 rows) chained with programmatic dependent launch.
+// The buckets differ in the token tile and therefore in how many stages of weights fit the ring: these shapes are
+// HBM-bound on the weights, and bytes in flight per SM are what saturates HBM.
 //
-//   warp 0    producer: TMA loads of the weight tile and the token tile per K block (5-stage ring)
-//   warp 1    TMEM allocation, MMA issue (one lane)
-//   warps 2-5 scale staging (sa * sb for the tile, transposed into shared memory), promotion, output
+//   warp 0     producer: TMA loads of the weight tile and the token tile per K block
+//   warps 1, 2 MMA issue, one lane each: warp 1 (which also owns the TMEM allocation) takes the even K blocks, warp 2
+//              the odd ones — consecutive K blocks go to different partial buffers, and a tcgen05.mma costs its
+//              issuing thread ~90 cycles against 64 cycles of tensor time for a 128 x 128 x 32 MMA
+//   warps 3(,4) scale loaders (two of them alternate chunks where registers allow): sa[token, kb] * sb[tile, kb] for 8 K blocks at a time, transposed to
+//              [kb][token] in a ring of chunks, so that the epilogue reads one broadcast float4 per 4 tokens and
+//              never waits on global memory, whatever K is
+//   then       promotion (partial * scale -> fp32 registers) and output through a per-warp shared-memory transpose:
+//              one set of four warps (the four TMEM lane quadrants) per 32 token columns, so that a warp holds
+//              32 accumulators, reads its share of a partial with ONE tcgen05.ld, and the sets hide each other's
+//              TMEM latency; for the narrow tiles two such groups take alternate tiles, which hides the per-tile
+//              latencies (work-list decode, output) that dominate when K is only 2-4 blocks
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "epilogue.cuh"
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
 namespace es_b200 {
 namespace bw {
 
-constexpr int THREADS = 192;
 constexpr int TILE_N = 128;
 constexpr int TILE_K = 128;
-constexpr int TOK_TILE = 128;
-constexpr int STAGES = 5;
 constexpr int W_BYTES = TILE_N * TILE_K;
-constexpr int X_BYTES = TOK_TILE * TILE_K;
-constexpr int STAGE_BYTES = W_BYTES + X_BYTES;     // 32 KB
-constexpr uint32_t TMEM_COLS = 256;                // two partial buffers of 128 columns
-constexpr int MAX_KT = 112;                        // K <= 14336: the per-tile scale table must fit shared memory
+constexpr int NPART = 4;             // TMEM partial buffers
+constexpr int CH_KT = 8;             // K blocks per scale chunk
+constexpr int MAX_NCH = 4;           // scale chunks in the ring (per shape: 2 or 4)
+constexpr int MAX_STAGES = 10;
+constexpr int EPI_TOK = 16;                          // tokens per pass through an epilogue warp's transposition tile
+constexpr int EPI_TILE_BYTES = EPI_TOK * 32 * 2;     // 1 KB
 
-constexpr uint32_t ERR_PRODUCER = 0x100u, ERR_MMA = 0x200u, ERR_EPILOGUE = 0x400u;
+constexpr uint32_t ERR_PRODUCER = 0x1000u, ERR_MMA = 0x2000u, ERR_EPILOGUE = 0x4000u, ERR_SCALES = 0x8000u;
 
 struct SharedCtl {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
-  uint64_t part_full[2];
-  uint64_t part_empty[2];
-  uint64_t epi_sync;            // 128 arrivals: rendezvous of the epilogue threads (bounded, unlike bar.sync)
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
+  uint64_t part_full[NPART];
+  uint64_t part_empty[NPART];     // one arrival per warp of the epilogue group that owns the tile
+  uint64_t chunk_full[MAX_NCH];   // 1 arrival: the chunk's scale loader
+  uint64_t chunk_empty[MAX_NCH];  // one arrival per warp of the epilogue group that owns the tile
+  uint64_t turn[2];               // turn[x]: epilogue group x may enter the K loop of its next tile
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
   int tile_prefix[ES_B200_MAX_EXPERTS + 1];
 };
+
+template <int TOK_TILE_, int STAGES_, int NCH_, int LOADERS_, int GROUPS_>
+struct Shape {
+  static constexpr int GROUPS = GROUPS_;                   // epilogue groups; consecutive tiles alternate between them
+  static constexpr int LOADERS = LOADERS_;                 // scale loader warps (1 or 2)
+  static constexpr int FIRST_EPI_WARP = 3 + LOADERS;
+  static constexpr int TOK_TILE = TOK_TILE_;               // token rows per tile = columns of one TMEM partial
+  static constexpr int STAGES = STAGES_;
+  static constexpr int NCH = NCH_;
+  static constexpr int GROUP_WARPS = 4 * (TOK_TILE / 32);  // 4 lane quadrants x sets of 32 token columns
+  static constexpr int EPI_WARPS = GROUPS * GROUP_WARPS;
+  static constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
+  static constexpr int X_BYTES = TOK_TILE * TILE_K;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr uint32_t TMEM_COLS = NPART * TOK_TILE;  // 128 / 256 / 512
+  static constexpr int CHUNK_FLOATS = CH_KT * TOK_TILE;
+  static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)NCH * CHUNK_FLOATS * 4 +
+                                       (size_t)EPI_WARPS * EPI_TILE_BYTES + sizeof(SharedCtl);
+  static_assert(NCH == 2 || NCH == 4, "ring slots are taken modulo a power of two");
+  static_assert(LOADERS == 1 || LOADERS == 2, "chunks alternate between at most two loaders");
+  static_assert(GROUPS == 1 || GROUPS == 2, "tiles alternate between at most two epilogue groups");
+  static_assert(STAGES <= MAX_STAGES, "ring too deep for the control block");
+  // A waiter may be at most one phase ahead of its mbarrier.  Each ring barrier therefore has ONE waiting role per
+  // revolution: K blocks (and chunks) alternate between two lanes (warps), so ring sizes must be even.
+  static_assert(STAGES % 2 == 0 && NPART % 2 == 0, "alternating owners need even rings");
+  static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzled tiles");
+  static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA per SM");
+};
+// 20 warps = 5 per scheduler leave 96 registers per thread; 21 would leave 80
+using ShapeTiny = Shape<32, 10, 4, 2, 2>;    // rows <= 32:   20 KB stages, 200 KB in flight; 13 warps
+using ShapeSmall = Shape<64, 8, 4, 1, 2>;    // rows 33..64:  24 KB stages; 20 warps
+using ShapeFull = Shape<128, 6, 2, 1, 1>;    // rows >= 65:   32 KB stages; 20 warps
 
 __device__ uint32_t g_status = 0;
 
@@ -53,6 +99,7 @@ struct TileInfo {
   int e, tt, nt, valid, n_mma, row0;
 };
 
+template <int TOK_TILE>
 __device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
                                                 const int* expert_offsets) {
   TileInfo ti;
@@ -69,35 +116,23 @@ __device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int nu
   return ti;
 }
 
-template <typename OutT>
-__device__ __forceinline__ OutT from_f32(float v);
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
-
-// Rendezvous of the 128 epilogue threads on an mbarrier, so that a thread whose partners gave up returns false
-// after the wait limit instead of blocking forever.
-__device__ __forceinline__ bool epilogue_rendezvous(uint64_t* bar, uint32_t& phase, volatile int* abort_flag) {
-  ptx::mbar_arrive(bar);
-  const bool ok = ptx::mbar_wait(bar, phase, abort_flag);
-  phase ^= 1u;
-  return ok;
-}
-
-template <typename OutT>
-__global__ void __launch_bounds__(THREADS, 1)
+template <typename OutT, class S>
+__global__ void __launch_bounds__(S::THREADS, 1)
 fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
                                 const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
                                 const __grid_constant__ CUtensorMap map_x128, const float* __restrict__ scales_a,
                                 const float* __restrict__ scales_b, OutT* __restrict__ d,
                                 const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                                int num_experts, int n, int k) {
+                                int num_experts, int n, int k, int min_rows, int max_rows, int wait_at_start) {
+  constexpr int TOK = S::TOK_TILE;
+  constexpr int STAGES = S::STAGES;
+  constexpr int NCH = S::NCH;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* chunks = reinterpret_cast<float*>(smem + (size_t)STAGES * S::STAGE_BYTES);        // [NCH][CH_KT][TOK]
+  uint8_t* epi_stage = reinterpret_cast<uint8_t*>(chunks + NCH * S::CHUNK_FLOATS);        // 1 KB per epilogue warp
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + (size_t)S::EPI_WARPS * EPI_TILE_BYTES);
   const int kt_count = k / TILE_K;
-  float* s_tile = reinterpret_cast<float*>(smem + (size_t)STAGES * STAGE_BYTES);          // [kt_count][128]
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + (size_t)STAGES * STAGE_BYTES + (size_t)kt_count * 512);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -106,11 +141,16 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
       ptx::mbar_init(&ctl->full[s], 1);
       ptx::mbar_init(&ctl->empty[s], 1);
     }
-    for (int p = 0; p < 2; ++p) {
+    for (int p = 0; p < NPART; ++p) {
       ptx::mbar_init(&ctl->part_full[p], 1);
-      ptx::mbar_init(&ctl->part_empty[p], 4);
+      ptx::mbar_init(&ctl->part_empty[p], S::GROUP_WARPS);
     }
-    ptx::mbar_init(&ctl->epi_sync, 128);
+    for (int c = 0; c < NCH; ++c) {
+      ptx::mbar_init(&ctl->chunk_full[c], 1);
+      ptx::mbar_init(&ctl->chunk_empty[c], S::GROUP_WARPS);
+    }
+    ptx::mbar_init(&ctl->turn[0], S::GROUP_WARPS);
+    ptx::mbar_init(&ctl->turn[1], S::GROUP_WARPS);
     ctl->abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&map_w);
@@ -120,14 +160,16 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
     ptx::prefetch_tensormap(&map_x128);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    ptx::tmem_alloc(&ctl->tmem_base, S::TMEM_COLS);
     ptx::tmem_relinquish();
   }
-  pdl_wait_prior_grid();
+  // The first kernel of a call waits for the stream's earlier work and then lets the other buckets' kernels start;
+  // those write disjoint rows of d and only wait for their predecessor before they exit (stream order).
+  if (wait_at_start) pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
   block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
-    return m > 0 ? ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles : 0;
+    return (m > 0 && m >= min_rows && m <= max_rows) ? ((m + TOK - 1) / TOK) * n_tiles : 0;
   });
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -139,12 +181,13 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
   volatile int* abort_flag = &ctl->abort_flag;
 
   if (warp == 0) {
+    // ------------------------------------------------------------------ producer
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_x128;
         const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : 128u;
         const uint32_t tx = W_BYTES + box_rows * TILE_K;
@@ -156,7 +199,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
             atomicOr(&g_status, ERR_PRODUCER);
             break;
           }
-          uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+          uint8_t* stage = smem + (size_t)s * S::STAGE_BYTES;
           ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
           ptx::tma_load_2d(stage, &map_w, &ctl->full[s], kt * TILE_K, w_row);
           ptx::tma_load_2d(stage + W_BYTES, xm, &ctl->full[s], kt * TILE_K, ti.row0);
@@ -164,32 +207,34 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------------ MMA issue: K blocks alternate between the
+    // two lanes; g counts K blocks over all tiles of this CTA (stage = g mod STAGES, partial = g mod 4)
     if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
-      int p = 0;
-      uint32_t p_ph = 0;
+      const int mine = warp - 1;
+      int g = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         const uint32_t idesc = ptx::make_idesc_f8(TILE_N, ti.n_mma);
-        for (int kt = 0; kt < kt_count; ++kt) {
+        for (int kt = 0; kt < kt_count; ++kt, ++g) {
+          if ((g & 1) != mine) continue;
+          const int s = g % STAGES;
+          const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+          const int p = g & (NPART - 1);
+          const uint32_t p_ph = (uint32_t)(g / NPART) & 1u;
           if (!ptx::mbar_wait(&ctl->part_empty[p], p_ph ^ 1u, abort_flag)) { ok = false; break; }
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
-          const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint32_t stage = ptx::smem_u32(smem + (size_t)s * S::STAGE_BYTES);
           const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
           const uint64_t b_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
-          const uint32_t d_tmem = tmem_base + p * 128;
+          const uint32_t d_tmem = tmem_base + p * TOK;
 #pragma unroll
           for (uint32_t j = 0; j < 4; ++j)
             ptx::tc_mma_f8(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, j != 0 ? 1u : 0u);
           ptx::tc_commit(&ctl->empty[s]);
           ptx::tc_commit(&ctl->part_full[p]);
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
-          p ^= 1;
-          if (p == 0) p_ph ^= 1u;
         }
         if (!ok) {
           *abort_flag = 1;
@@ -197,34 +242,103 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
         }
       }
     }
-  } else {
-    const int q = warp & 3;
-    const int etid = threadIdx.x - 64;     // 0..127 among the epilogue threads
-    int p = 0;
-    uint32_t p_ph = 0;
-    bool alive = true;
-    uint32_t sync_ph = 0;
-    for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x) {
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-      // scale table of the tile: s_tile[kt][tok] = sa[row0 + tok, kt] * sb[e, nt, kt]
-      if (!epilogue_rendezvous(&ctl->epi_sync, sync_ph, abort_flag)) break;   // all done with the previous table
-      {
-        const float* sb_row = scales_b + ((int64_t)ti.e * n_tiles + ti.nt) * kt_count;
-        if (etid < ti.valid) {
-          const float* sa_row = scales_a + (int64_t)(ti.row0 + etid) * kt_count;
-          for (int kt = 0; kt < kt_count; ++kt) s_tile[kt * 128 + etid] = __ldg(sa_row + kt) * __ldg(sb_row + kt);
-        } else {
-          for (int kt = 0; kt < kt_count; ++kt) s_tile[kt * 128 + etid] = 0.f;
-        }
-      }
-      if (!epilogue_rendezvous(&ctl->epi_sync, sync_ph, abort_flag)) break;
-
-      float acc[128];
+  } else if (warp < S::FIRST_EPI_WARP) {
+    // ------------------------------------------------------------------ scale loaders: chunks alternate between the
+    // two warps; c counts chunks over all tiles of this CTA (ring slot = c mod NCH)
+    constexpr int LMASK = S::LOADERS - 1;     // 0: one loader takes every chunk; 1: the two loaders alternate
+    const int mine = warp - 3;
+    int c = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      const int chunks_in_tile = (kt_count + CH_KT - 1) / CH_KT;
+      // this warp's chunks of the tile: c, c+1, .. with (c & 1) == mine
+      if (chunks_in_tile == 1 && (c & LMASK) != mine) { ++c; continue; }   // common for small K: skip the decode too
+      const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const float* sb_row = scales_b + ((int64_t)ti.e * n_tiles + ti.nt) * kt_count;
+      for (int kt0 = 0; kt0 < kt_count; kt0 += CH_KT, ++c) {
+        if ((c & LMASK) != mine) continue;
+        const int cs = c & (NCH - 1);
+        const uint32_t c_ph = (uint32_t)(c / NCH) & 1u;
+        // the loads do not depend on the ring slot: issue them before waiting for it
+        const int nk = kt_count - kt0 < CH_KT ? kt_count - kt0 : CH_KT;
+        float sb[CH_KT];
 #pragma unroll
-      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+        for (int i = 0; i < CH_KT; ++i) sb[i] = i < nk ? __ldg(sb_row + kt0 + i) : 0.f;
+        float sa[TOK / 32][CH_KT];
+#pragma unroll
+        for (int u = 0; u < TOK / 32; ++u) {
+          const int tok = u * 32 + lane;
+          const float* sa_row = scales_a + (int64_t)(ti.row0 + tok) * kt_count + kt0;
+#pragma unroll
+          for (int i = 0; i < CH_KT; ++i) sa[u][i] = (tok < ti.valid && i < nk) ? __ldg(sa_row + i) : 0.f;
+        }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctl->chunk_empty[cs], c_ph ^ 1u, abort_flag))) {
+          ok = false;
+          if (lane == 0) {
+            *abort_flag = 1;
+            atomicOr(&g_status, ERR_SCALES);
+          }
+          break;
+        }
+        float* chunk = chunks + cs * S::CHUNK_FLOATS;
+#pragma unroll
+        for (int u = 0; u < TOK / 32; ++u) {
+          const int tok = u * 32 + lane;
+          if (u * 32 < ti.n_mma) {                 // columns past n_mma are never read (warp-uniform)
+#pragma unroll
+            for (int i = 0; i < CH_KT; ++i) chunk[i * TOK + tok] = sa[u][i] * sb[i];
+          }
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctl->chunk_full[cs]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ promotion and output (warps 5..)
+    // Consecutive tiles alternate between the epilogue groups: while one group converts and stores its tile (and
+    // decodes the next), the other is already accumulating the following tile's partials.  The K loops themselves
+    // are strictly serial (turn barriers): a group that waited on part_full / chunk_full for a tile further ahead
+    // would be more than one phase ahead of those barriers, and a parity wait cannot tell phases n and n+2 apart.
+    const int q = warp & 3;                           // TMEM lane quadrant of this warp
+    const int group = (warp - S::FIRST_EPI_WARP) / S::GROUP_WARPS;
+    const int col0 = (((warp - S::FIRST_EPI_WARP) % S::GROUP_WARPS) >> 2) * 32;   // this warp's 32 token columns
+    OutT* stage_warp = reinterpret_cast<OutT*>(epi_stage) + (warp - S::FIRST_EPI_WARP) * (EPI_TOK * 32);
+    const int part = lane & 3;
+    int g = 0;                                        // K blocks over all tiles of this CTA
+    int c = 0;                                        // scale chunks over all tiles of this CTA
+    bool alive = true;
+    uint32_t turn_ph = 0;
+    int tile_index = 0;
+    for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x, ++tile_index) {
+      if ((tile_index & (S::GROUPS - 1)) != group) {   // the other group's tile
+        g += kt_count;
+        c += (kt_count + CH_KT - 1) / CH_KT;
+        continue;
+      }
+      const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const bool has_cols = col0 < ti.n_mma;          // warp-uniform: a set past the tile's tokens only keeps the
+                                                      // barriers moving
+      float acc[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+      if (S::GROUPS == 2 && tile_index > 0) {          // the other group has left the K loop of the previous tile
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctl->turn[group], turn_ph, abort_flag))) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            atomicOr(&g_status, ERR_EPILOGUE);
+          }
+          break;
+        }
+        turn_ph ^= 1u;
+      }
 
-      for (int kt = 0; kt < kt_count; ++kt) {
-        const bool got = ptx::mbar_wait(&ctl->part_full[p], p_ph, abort_flag);
+      for (int kt = 0; kt < kt_count; ++kt, ++g) {
+        const int ki = kt & (CH_KT - 1);
+        const int cs = c & (NCH - 1);
+        const int p = g & (NPART - 1);
+        bool got = true;
+        if (ki == 0) got = ptx::mbar_wait(&ctl->chunk_full[cs], (uint32_t)(c / NCH) & 1u, abort_flag);
+        got = got && ptx::mbar_wait(&ctl->part_full[p], (uint32_t)(g / NPART) & 1u, abort_flag);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) {
             *abort_flag = 1;
@@ -233,39 +347,56 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
           alive = false;
           break;
         }
-        ptx::tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + p * 128 + ((uint32_t)(q * 32) << 16);
-        const float4* srow = reinterpret_cast<const float4*>(s_tile + kt * 128);
+        uint32_t v[32];
+        if (has_cols) {
+          ptx::tc_fence_after_sync();
+          ptx::tc_ld_32x32b_x32(tmem_base + p * TOK + col0 + ((uint32_t)(q * 32) << 16), v);
+          ptx::tc_wait_ld();
+          ptx::tc_fence_before_sync();
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctl->part_empty[p]);      // the tensor core may overwrite this partial
+        if (has_cols) {
+          const float4* srow = reinterpret_cast<const float4*>(chunks + cs * S::CHUNK_FLOATS + ki * TOK + col0);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          if (c * 16 < ti.n_mma) {     // warp-uniform
-            uint32_t v[16];
-            ptx::tc_ld_32x32b_x16(taddr + c * 16, v);
-            ptx::tc_wait_ld();
-            if ((c + 1) * 16 >= ti.n_mma) {
-              // last read of this partial buffer by this warp: the tensor core may overwrite it
-              ptx::tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) ptx::mbar_arrive(&ctl->part_empty[p]);
-            }
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const float4 sc = srow[c * 4 + g];      // same address in every lane: broadcast
-              acc[c * 16 + g * 4 + 0] = fmaf(__uint_as_float(v[g * 4 + 0]), sc.x, acc[c * 16 + g * 4 + 0]);
-              acc[c * 16 + g * 4 + 1] = fmaf(__uint_as_float(v[g * 4 + 1]), sc.y, acc[c * 16 + g * 4 + 1]);
-              acc[c * 16 + g * 4 + 2] = fmaf(__uint_as_float(v[g * 4 + 2]), sc.z, acc[c * 16 + g * 4 + 2]);
-              acc[c * 16 + g * 4 + 3] = fmaf(__uint_as_float(v[g * 4 + 3]), sc.w, acc[c * 16 + g * 4 + 3]);
-            }
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 sc = srow[j4];                // same address in every lane: broadcast
+            acc[j4 * 4 + 0] = fmaf(__uint_as_float(v[j4 * 4 + 0]), sc.x, acc[j4 * 4 + 0]);
+            acc[j4 * 4 + 1] = fmaf(__uint_as_float(v[j4 * 4 + 1]), sc.y, acc[j4 * 4 + 1]);
+            acc[j4 * 4 + 2] = fmaf(__uint_as_float(v[j4 * 4 + 2]), sc.z, acc[j4 * 4 + 2]);
+            acc[j4 * 4 + 3] = fmaf(__uint_as_float(v[j4 * 4 + 3]), sc.w, acc[j4 * 4 + 3]);
           }
         }
-        p ^= 1;
-        if (p == 0) p_ph ^= 1u;
+        if (ki == CH_KT - 1 || kt == kt_count - 1) {          // done with this scale chunk
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&ctl->chunk_empty[cs]);
+          ++c;
+        }
       }
       if (!alive) break;
-      OutT* dcol = d + (int64_t)ti.row0 * n + (ti.nt * TILE_N + q * 32 + lane);
+      if (S::GROUPS == 2) {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctl->turn[group ^ 1]);
+      }
+      // output: this warp's 32 tokens x 32 n, 16 tokens at a time through its 1 KB tile, 128-bit stores (4 lanes per
+      // 64-byte row piece)
+      if (col0 < ti.valid) {
+        OutT* dst = d + (int64_t)(ti.row0 + col0) * n + (ti.nt * TILE_N + q * 32);
 #pragma unroll
-      for (int j = 0; j < 128; ++j)
-        if (j < ti.valid) dcol[(int64_t)j * n] = from_f32<OutT>(acc[j]);
+        for (int h = 0; h < 32 / EPI_TOK; ++h) {
+#pragma unroll
+          for (int j = 0; j < EPI_TOK; ++j) stage_warp[j * 32 + lane] = out_from_f32<OutT>(acc[h * EPI_TOK + j]);
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < EPI_TOK / 8; ++it) {
+            const int tok = it * 8 + (lane >> 2);
+            const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
+            const int row = col0 + h * EPI_TOK + tok;
+            if (row < ti.valid) *reinterpret_cast<uint4*>(dst + (int64_t)(h * EPI_TOK + tok) * n + part * 8) = val;
+          }
+          __syncwarp();
+        }
+      }
     }
   }
 
@@ -273,19 +404,18 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    ptx::tmem_dealloc(tmem_base, S::TMEM_COLS);
   }
+  if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
 }
 
-template <typename OutT>
+template <typename OutT, class S>
 int launch(const void* a, const void* b, const float* sa, const float* sb, void* d, const int32_t* ps,
-           const int32_t* eo, int num_experts, int64_t num_rows, int n, int k, cudaStream_t stream) {
+           const int32_t* eo, int num_experts, int64_t num_rows, int n, int k, int min_rows, int max_rows,
+           bool first_of_call, cudaStream_t stream) {
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
-  const int kt_count = k / TILE_K;
-  if (kt_count > MAX_KT)
-    return fail(ES_B200_ERR_INVALID_ARGUMENT, "fp8 blockwise grouped GEMM supports k <= %d (got %d)", MAX_KT * TILE_K, k);
 
   CUtensorMap map_w, map_x[4];
   rc = make_tensormap_u8_sw128(&map_w, b, (uint64_t)num_experts * n, (uint64_t)k, TILE_N);
@@ -295,22 +425,21 @@ int launch(const void* a, const void* b, const float* sa, const float* sb, void*
     rc = make_tensormap_u8_sw128(&map_x[i], a, (uint64_t)num_rows, (uint64_t)k, boxes[i]);
     if (rc != ES_B200_OK) return rc;
   }
-  auto kernel = fp8_blockwise_grouped_mm_kernel<OutT>;
-  const size_t smem_bytes = 1024 + (size_t)STAGES * STAGE_BYTES + (size_t)kt_count * 512 + sizeof(SharedCtl);
-  static size_t configured[64] = {0};   // largest dynamic shared memory size set so far, per device
+  auto kernel = fp8_blockwise_grouped_mm_kernel<OutT, S>;
+  static bool configured[64] = {false};
   int dev = 0;
   ES_CUDA_TRY(cudaGetDevice(&dev));
-  if (configured[dev & 63] < smem_bytes) {
-    ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    configured[dev & 63] = smem_bytes;
+  if (!configured[dev & 63]) {
+    ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES));
+    configured[dev & 63] = true;
   }
-  const int64_t max_tiles = ((num_rows + TOK_TILE - 1) / TOK_TILE + num_experts) * (int64_t)(n / TILE_N);
+  const int64_t max_tiles = ((num_rows + S::TOK_TILE - 1) / S::TOK_TILE + num_experts) * (int64_t)(n / TILE_N);
   const int grid = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.blockDim = dim3(S::THREADS);
+  cfg.dynamicSmemBytes = S::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -318,8 +447,21 @@ int launch(const void* a, const void* b, const float* sa, const float* sb, void*
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sa, sb,
-                                 static_cast<OutT*>(d), ps, eo, num_experts, n, k));
+                                 static_cast<OutT*>(d), ps, eo, num_experts, n, k, min_rows, max_rows,
+                                 first_of_call ? 1 : 0));
   return ES_B200_OK;
+}
+
+template <typename OutT>
+int launch_buckets(const void* a, const void* b, const float* sa, const float* sb, void* d, const int32_t* ps,
+                   const int32_t* eo, int num_experts, int64_t num_rows, int n, int k, cudaStream_t stream) {
+  // One kernel per row-count bucket, back to back with programmatic dependent launch; each filters the experts in
+  // its own scan.  A bucket that even the host-known upper bound of rows per expert cannot reach is not launched.
+  int rc = launch<OutT, ShapeTiny>(a, b, sa, sb, d, ps, eo, num_experts, num_rows, n, k, 1, 32, true, stream);
+  if (rc != ES_B200_OK || num_rows <= 32) return rc;
+  rc = launch<OutT, ShapeSmall>(a, b, sa, sb, d, ps, eo, num_experts, num_rows, n, k, 33, 64, false, stream);
+  if (rc != ES_B200_OK || num_rows <= 64) return rc;
+  return launch<OutT, ShapeFull>(a, b, sa, sb, d, ps, eo, num_experts, num_rows, n, k, 65, 0x7fffffff, false, stream);
 }
 
 int read_and_clear_status(uint32_t* out) {
@@ -352,12 +494,13 @@ extern "C" int es_b200_fp8_blockwise_grouped_mm(const void* a, const void* b, co
   ES_REQUIRE((int64_t)num_experts * n < (int64_t)1 << 31, "num_experts * n out of range");
   if (num_experts == 0 || num_rows == 0) return ES_B200_OK;
   ES_REQUIRE(a && b && scales_a && scales_b && d && problem_sizes && expert_offsets, "null pointer argument");
-  ES_REQUIRE(aligned16(a) && aligned16(b), "a and b must be 16-byte aligned");
+  ES_REQUIRE(aligned16(a) && aligned16(b) && aligned16(d), "a, b and d must be 16-byte aligned");
   ES_REQUIRE((reinterpret_cast<uintptr_t>(scales_a) & 3u) == 0 && (reinterpret_cast<uintptr_t>(scales_b) & 3u) == 0,
              "scales must be 4-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (out_dtype == ES_B200_BF16)
-    return bw::launch<__nv_bfloat16>(a, b, scales_a, scales_b, d, problem_sizes, expert_offsets, num_experts, num_rows,
-                                     n, k, s);
-  return bw::launch<__half>(a, b, scales_a, scales_b, d, problem_sizes, expert_offsets, num_experts, num_rows, n, k, s);
+    return bw::launch_buckets<__nv_bfloat16>(a, b, scales_a, scales_b, d, problem_sizes, expert_offsets, num_experts,
+                                             num_rows, n, k, s);
+  return bw::launch_buckets<__half>(a, b, scales_a, scales_b, d, problem_sizes, expert_offsets, num_experts, num_rows,
+                                    n, k, s);
 }

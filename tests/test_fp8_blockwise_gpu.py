@@ -39,6 +39,23 @@ def test_blockwise_matches_oracle(counts, N, K, out_dtype):
     _check(inp, d, out_dtype)
 
 
+@pytest.mark.parametrize("lo,hi,E,N,K", [
+    (1, 32, 96, 1024, 1280),      # <= 32 rows: 768 tiles of 10 K blocks (two scale chunks per tile)
+    (33, 64, 96, 1024, 512),      # 33..64 rows: tiles of 4 K blocks = one pass over the TMEM partials
+    (65, 200, 40, 1024, 1152),    # >= 65 rows, some experts with two token tiles
+    (1, 150, 120, 896, 384),      # all three buckets in one call
+])
+def test_blockwise_many_tiles_per_cta(lo, hi, E, N, K):
+    """More tiles than SMs, so that every CTA walks several tiles: covers the hand-over between the two epilogue
+    groups, the rings wrapping across tile boundaries, and the chained per-bucket launches."""
+    import random
+    rnd = random.Random(11)
+    counts = [rnd.randint(lo, hi) for _ in range(E)]
+    inp = C.fp8_blockwise_inputs(counts, N, K, seed=5)
+    d = C.run_fp8_blockwise_op(inp)
+    _check(inp, d, torch.bfloat16)
+
+
 def test_blockwise_reference_test_shapes():
     """The reference's own test draws n, k in 128*[1,64], m in [1,256], E in {8..128}; one seeded draw of that family."""
     import random
