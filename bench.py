@@ -48,6 +48,13 @@ WORKLOADS = {
     "quant": (256, 32768, 0, 7168, "grouped MXFP8 quantisation: bf16 [32768, 7168], E=256, Zipf(1.2) counts, "
                                    "e4m3 codes + swizzled UE8M0 scales"),
     "qwen3_ep": (128, 0, 0, 0, "Qwen3-30B-A3B-shaped MoE layer with expert parallelism (N >= 2)"),
+    # the reference's own published benchmark (benchmark/benchmark_es_fp8_blockwise_moe.py: uniform-random top-8
+    # routing, bf16 output), FP8-blockwise op; T = batch x top-8.  H200 numbers of the reference for these two points:
+    # 264.8 us = 113.6 TFLOP/s and 187.2 us = 80.3 TFLOP/s (media/performance_data/H200_bench.log:14-16, 62-64)
+    "blockwise_gate_up": (256, 4096, 512, 7168, "FP8-blockwise grouped GEMM, DeepSeek-R1 gate_up TP8 of the reference's "
+                                                "benchmark: E=256, batch 512 x top-8 uniform-random routing, n=512, k=7168"),
+    "blockwise_down": (256, 4096, 7168, 256, "FP8-blockwise grouped GEMM, DeepSeek-R1 down TP8 of the reference's "
+                                             "benchmark: E=256, batch 512 x top-8 uniform-random routing, n=7168, k=256"),
     "quant_small": (64, 8192, 0, 7168, "grouped MXFP8 quantisation at 1/4 scale for profiler captures: bf16 "
                                        "[8192, 7168], E=64"),
 }
@@ -374,6 +381,114 @@ def bench_quant(args, E, T, K, desc, device, rank, world, dist):
         dist.destroy_process_group()
 
 
+def reference_blockwise(args, E, T, N, K, desc):
+    """CPU arm of the blockwise workloads: the reference test's torch dequant + matmul (restated in oracle/) on the
+    first experts of the same routing, as many as fit about a second per step, all host threads."""
+    from oracle import grouped_gemm_oracle as G
+    rng = np.random.default_rng(3)
+    counts = np.bincount(rng.integers(0, E, size=T), minlength=E).astype(np.int64)
+    n_exp = int(max(1, min(E, 0.05e12 / max(1.0, 2.0 * counts.mean() * N * K + 4.0 * N * K))))
+    counts = counts[:n_exp]
+    rows = int(counts.sum())
+    g = torch.Generator(); g.manual_seed(5)
+    a = torch.randint(0, 0x78, (rows, K), dtype=torch.uint8, generator=g)
+    w = torch.randint(0, 0x78, (n_exp, N, K), dtype=torch.uint8, generator=g)
+    sa = torch.rand((rows, K // 128), generator=g) * 0.01 + 0.001
+    sb = torch.rand((n_exp, N // 128, K // 128), generator=g) * 0.01 + 0.001
+    eo = np.zeros(n_exp, dtype=np.int64); eo[1:] = np.cumsum(counts)[:-1]
+    ps = np.stack([counts, np.full(n_exp, N), np.full(n_exp, K)], axis=1)
+    rates, secs = [], 0.0
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        G.fp8_blockwise_grouped_mm(a, w, sa, sb, ps, eo)
+        secs = time.perf_counter() - t0
+        if i >= args.warmup:
+            rates.append(2.0 * rows * N * K / secs / 1e12)
+    v = float(np.mean(rates)) if rates else 0.0
+    cores = torch.get_num_threads()
+    line = {"impl": "reference", "metric": "FP8-blockwise grouped GEMM TFLOPS", "value": v, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 2.0 * T * N * K / (v * 1e12) * 1e3 if v else None, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp32 block scales", "data": "synthetic",
+            "config": {"workload": desc},
+            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                             "sample": f"first {n_exp} of {E} experts ({rows} rows), {secs:.2f} s per step"},
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+PUBLISHED_H200_TFLOPS = {"blockwise_gate_up": 113.6, "blockwise_down": 80.3}
+
+
+def bench_blockwise(args, E, T, N, K, desc, device, rank, world, dist):
+    """es_fp8_blockwise_scaled_grouped_mm on a shape of the reference's benchmark script; experts sharded E/N per GPU."""
+    from expert_specialization_moe_b200 import es_fp8_blockwise_scaled_grouped_mm as op
+    rng = np.random.default_rng(3)
+    ids = rng.integers(0, E, size=T)                        # uniform-random top-k routing, as the reference benchmark
+    counts_all = np.bincount(ids, minlength=E).astype(np.int64)
+    el = E // world
+    counts = counts_all[rank * el:(rank + 1) * el]
+    rows = int(counts.sum())
+    g = torch.Generator(device=device); g.manual_seed(11 + rank)
+    # random finite e4m3 codes and positive scales: timing does not depend on the values
+    w = torch.randint(0, 0x78, (el, N, K), dtype=torch.uint8, device=device, generator=g).view(torch.float8_e4m3fn)
+    a = torch.randint(0, 0x78, (max(rows, 1), K), dtype=torch.uint8, device=device, generator=g).view(torch.float8_e4m3fn)[:rows]
+    sb = torch.rand((el, N // 128, K // 128), device=device, generator=g) * 0.01 + 0.001
+    sa = torch.rand((rows, K // 128), device=device, generator=g) * 0.01 + 0.001
+    d = torch.empty((rows, N), dtype=torch.bfloat16, device=device)
+    eo = np.zeros(el, dtype=np.int32); eo[1:] = np.cumsum(counts)[:-1]
+    ps = np.stack([counts, np.full(el, N), np.full(el, K)], axis=1).astype(np.int32)
+    ps, eo = torch.from_numpy(ps).to(device), torch.from_numpy(eo).to(device)
+    st = torch.full((el,), K, dtype=torch.int64, device=device)
+    ws = torch.empty(16, dtype=torch.uint8, device=device)
+    step = lambda: op(d, a, w.transpose(1, 2), sa, sb.transpose(1, 2), st, st, st, ps, eo, ws)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(device.index or 0)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1) / args.steps
+    abytes_local = el * N * K + rows * K + rows * N * 2 + 4 * (el * (N // 128) * (K // 128) + rows * (K // 128))
+    stats = torch.tensor([ms], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peak, peak_kind = peak_hbm()
+        achieved = abytes_local / (ms * 1e-3) / 1e9
+        value = 2.0 * T * N * K / (float(stats[0]) * 1e-3) / 1e12
+        buckets = 1 + (counts.max() > 32) + (counts.max() > 64)
+        line = {"metric": "FP8-blockwise grouped GEMM TFLOPS", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(stats[0]), "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": value / PUBLISHED_H200_TFLOPS[args.workload],
+                "vs_baseline_note": "published number is the reference's Hopper kernel on H200",
+                "dtype": "fp8_e4m3 x fp32 block scales", "data": "synthetic",
+                "config": {"workload": desc, "experts_per_gpu": el, "out_dtype": "bf16",
+                           "l2": "inputs larger than L2 (weights %.2f GB per GPU), no flush" % (el * N * K / 1e9)},
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "traffic": read_traffic(f"{args.workload}_n{world}"), "peak_kind": peak_kind,
+                             "algorithmic_bytes": abytes_local, "kernel": "fp8_blockwise_grouped_mm_kernel (per-bucket launches)",
+                             "kernel_ms": ms},
+                "clocks": clocks, "gpu_launches": int(args.steps * buckets)}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
@@ -405,6 +520,8 @@ def main():
         # the reference's CPU path, bounded sample per step; rank 0 only
         if rank != 0:
             return
+        if args.workload.startswith("blockwise"):
+            return reference_blockwise(args, E, T, N, K, desc)
         rates = []
         cores = os.cpu_count() or 1
         # the whole run (warm-up + steps) is kept to about two minutes: each step times one pass over a sample sized
@@ -446,6 +563,8 @@ def main():
         return bench_quant(args, E, T, K, desc, device, rank, world, dist)
     if args.workload == "qwen3_ep":
         return bench_ep_layer(args, device, rank, world, dist)
+    if args.workload.startswith("blockwise"):
+        return bench_blockwise(args, E, T, N, K, desc, device, rank, world, dist)
 
     # expert-parallel shard: E/world experts per rank
     assert E % world == 0
