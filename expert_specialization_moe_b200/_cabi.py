@@ -39,6 +39,17 @@ def _declare(lib):
     lib.es_b200_fp8_blockwise_grouped_mm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                                      c_size_t, c_void_p]
+    lib.es_b200_ep_dispatch_quant_push.restype = c_int
+    lib.es_b200_ep_dispatch_quant_push.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, POINTER(c_void_p),
+                                                   POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_int, c_int,
+                                                   c_int, c_int64, c_int64, c_void_p]
+    lib.es_b200_ep_combine_push.restype = c_int
+    lib.es_b200_ep_combine_push.argtypes = [c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int64, c_int64,
+                                            c_int, c_int, c_void_p]
+    lib.es_b200_ep_topk_weighted_sum.restype = c_int
+    lib.es_b200_ep_topk_weighted_sum.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.es_b200_ep_barrier.restype = c_int
+    lib.es_b200_ep_barrier.argtypes = [POINTER(c_void_p), c_int, c_int, c_void_p]
     lib.es_b200_check_status.restype = c_int
     lib.es_b200_check_status.argtypes = [c_void_p, POINTER(c_uint32)]
 

@@ -334,6 +334,9 @@ int launch_fp16(const void*, const void*, const uint8_t*, const uint8_t*, void*,
                 const int32_t*, int, int64_t, int, int, int64_t, int, int, cudaStream_t);
 int read_and_clear_status(uint32_t* out);
 }  // namespace mm2
+namespace ep {    // expert-parallel dispatch / combine kernels (ep_dispatch_combine.cu)
+int read_and_clear_status(uint32_t* out);
+}
 namespace bw {    // FP8-blockwise kernel (fp8_blockwise_grouped_mm.cu)
 int read_and_clear_status(uint32_t* out);
 }
@@ -424,7 +427,12 @@ extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {
   rc2 = bw::read_and_clear_status(&v2);
   if (rc2 != ES_B200_OK) return rc2;
   v |= v2;
+  rc2 = ep::read_and_clear_status(&v2);
+  if (rc2 != ES_B200_OK) return rc2;
+  v |= v2;
   if (raw_status) *raw_status = v;
-  if (v != 0) return fail(ES_B200_ERR_DEVICE_TIMEOUT, "a bounded device-side wait gave up (status bits 0x%x)", v);
+  if (v != 0)
+    return fail(ES_B200_ERR_DEVICE_TIMEOUT,
+                "a bounded device-side wait gave up or an index was out of range (status bits 0x%x)", v);
   return ES_B200_OK;
 }

@@ -11,6 +11,11 @@ compute on each rank's expert shard.  Nothing here computes a GEMM itself.
     y      = combine(y_e, plan, topk_weights)               # rows return and are summed per token with their weights
 
 Expert e lives on rank e // (E / G) (contiguous shards), local index e % (E / G).
+
+`FusedExchange` is the same layer without the all-to-alls: every rank quantises its tokens once and stores codes,
+scales and return addresses straight into the owners' receive buffers over NVLink (peer-mapped symmetric memory),
+the expert outputs are stored straight back into the senders' (token, j) slots, and the only collective left is an
+all-gather of the per-expert counts.  Nothing in it needs a size on the host, so a layer is a fixed sequence of launches.
 """
 from __future__ import annotations
 
@@ -120,6 +125,46 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.silu(gate_up[:, :i].float()).mul_(gate_up[:, i:].float()).to(gate_up.dtype)
 
 
+def routing_tables(topk_ids: torch.Tensor, counts_all: torch.Tensor, rank: int, hidden: int):
+    """Where every (token, j) pair of THIS rank goes, and what this rank's experts receive — tensor arithmetic only
+    (no host synchronisation; runs on CPU tensors too).
+
+    topk_ids [tokens, topk] expert ids; counts_all [G, E]: counts_all[s, e] = pairs rank s routes to expert e.
+    On the owner, the rows of one expert are ordered by source rank, inside a source by (token, j) order.
+    Returns a dict of tensors: dst_rank, dst_row (int32 [tokens*topk]), dst_scale_offset (int64: byte offset of the
+    row's scale word for K tile 0 in the owner's swizzled scale buffer), rows (int32 [E_local], m_e of my experts),
+    expert_offsets, blockscale_offsets (int32 [E_local]), total_rows (int32 [1])."""
+    world, num_experts = counts_all.shape
+    e_local = num_experts // world
+    kt = hidden // 128
+    counts_all = counts_all.to(torch.int64)
+    m = counts_all.sum(0)                                                    # rows per expert on its owner
+    m_owner = m.view(world, e_local)
+    eo_all = (torch.cumsum(m_owner, 1) - m_owner).reshape(-1)               # row offset of expert e on its owner
+    mp = _align128(m_owner)
+    bo_all = (torch.cumsum(mp, 1) - mp).reshape(-1)                         # scale-row offset of expert e on its owner
+    src_off = torch.cumsum(counts_all, 0) - counts_all                      # [G, E]: rows of lower ranks in expert e
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    pairs = flat.numel()
+    order = torch.sort(flat, stable=True).indices
+    mine = counts_all[rank]
+    start = torch.cumsum(mine, 0) - mine
+    pos_sorted = torch.arange(pairs, device=flat.device) - start[flat[order]]
+    pos = torch.empty_like(pos_sorted)
+    pos[order] = pos_sorted                                                  # rank of the pair among my pairs to its expert
+    r_local = src_off[rank][flat] + pos                                      # row inside the expert, on the owner
+    dst_rank = torch.div(flat, e_local, rounding_mode="floor")
+    dst_row = eo_all[flat] + r_local
+    sf_off = (bo_all[flat] * (hidden // 32) + (r_local >> 7) * (kt * 512) + (r_local & 31) * 16
+              + ((r_local & 127) >> 5) * 4)
+    lo, hi = rank * e_local, (rank + 1) * e_local
+    return {
+        "dst_rank": dst_rank.to(torch.int32), "dst_row": dst_row.to(torch.int32), "dst_scale_offset": sf_off,
+        "rows": m[lo:hi].to(torch.int32), "expert_offsets": eo_all[lo:hi].to(torch.int32),
+        "blockscale_offsets": bo_all[lo:hi].to(torch.int32), "total_rows": m[lo:hi].sum().to(torch.int32).reshape(1),
+    }
+
+
 class ExpertShard:
     """MXFP8 weights of this rank's experts: gate_up [E_local, 2I, H] and down [E_local, H, I], e4m3 + swizzled UE8M0,
     quantised once with the grouped quant operator (as the reference's own test quantises weights:
@@ -143,6 +188,28 @@ class ExpertShard:
         sf = torch.zeros((e * n, k // 32), dtype=torch.uint8, device=dev)
         quant(w.reshape(e * n, k).contiguous(), ps, off, off, codes, sf)
         return codes.view(e, n, k), sf
+
+    def forward_codes(self, a: torch.Tensor, sfa: torch.Tensor, rows: torch.Tensor, eo: torch.Tensor,
+                      bo: torch.Tensor, work: dict) -> torch.Tensor:
+        """a [capacity, H] e4m3 + sfa (swizzled) as delivered by FusedExchange.dispatch, grouped by local expert with
+        `rows[e]` valid rows at expert_offsets eo / blockscale_offsets bo (all on the device).  `work` caches the
+        capacity-sized intermediates.  Returns [capacity, H] (rows past the valid ones are undefined)."""
+        from .ops import es_sm100_mxfp8_blockscaled_grouped_mm as mm
+        from .ops import es_sm100_mxfp8_silu_mul_grouped_quant as silu_mul_quant
+        cap, dev = a.shape[0], a.device
+        if work.get("cap") != cap:
+            work.clear()
+            work.update(cap=cap,
+                        h1=torch.empty((cap, self.n1), dtype=torch.bfloat16, device=dev),
+                        a2=torch.empty((cap, self.i), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
+                        sfa2=torch.zeros((sfa.shape[0], self.i // 32), dtype=torch.uint8, device=dev),
+                        out=torch.empty((cap, self.h), dtype=torch.bfloat16, device=dev))
+        ps1 = torch.stack([rows, torch.full_like(rows, self.n1), torch.full_like(rows, self.h)], dim=1).contiguous()
+        ps2 = torch.stack([rows, torch.full_like(rows, self.h), torch.full_like(rows, self.i)], dim=1).contiguous()
+        mm(work["h1"], a, self.w1.transpose(1, 2), sfa, self.sf1, ps1, eo, bo)
+        silu_mul_quant(work["h1"], ps2, eo, bo, work["a2"], work["sfa2"])
+        mm(work["out"], work["a2"], self.w2.transpose(1, 2), work["sfa2"], self.sf2, ps2, eo, bo)
+        return work["out"]
 
     def forward(self, x: torch.Tensor, plan: DispatchPlan) -> torch.Tensor:
         """x [rows_in, H] bf16 grouped by local expert -> [rows_in, H] bf16."""
@@ -174,3 +241,91 @@ def moe_forward(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Ten
     rows = dispatch(x, plan, group)
     y = expert_fn(rows, plan)
     return combine(y, plan, topk_weights, group)
+
+
+class FusedExchange:
+    """Dispatch and combine of one MoE layer over peer memory (see the module docstring).  One instance per rank holds
+    one symmetric allocation: receive buffers for codes [capacity, H], swizzled scales, return addresses [capacity, 2],
+    and the (token, j) slots [tokens * topk, H] the expert outputs come back to.  `capacity` defaults to the worst
+    case (every pair of every rank routed to this rank)."""
+
+    def __init__(self, num_experts: int, topk: int, tokens: int, hidden: int, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None, capacity_rows: Optional[int] = None,
+                 dtype: torch.dtype = torch.bfloat16):
+        import ctypes
+        import torch.distributed._symmetric_memory as symm
+        from . import _cabi
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        assert num_experts % self.world == 0 and hidden % 128 == 0
+        self.num_experts, self.topk, self.tokens, self.hidden, self.dtype = num_experts, topk, tokens, hidden, dtype
+        self.e_local = num_experts // self.world
+        self.capacity = int(capacity_rows or self.world * tokens * topk)
+        self.scale_rows = (self.capacity + 128 * self.e_local + 127) // 128 * 128
+        self.scale_bytes = self.scale_rows * (hidden // 32)
+        sizes = [self.capacity * hidden, self.scale_bytes, self.capacity * 8, tokens * topk * hidden * 2, 17 * 4]
+        offs, total = [], 0
+        for sz in sizes:
+            offs.append(total)
+            total += (sz + 255) // 256 * 256
+        self.buf = symm.empty((total,), dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.hdl = symm.rendezvous(self.buf, self.group)
+        self.codes = self.buf[offs[0]:offs[0] + sizes[0]].view(torch.float8_e4m3fn).view(self.capacity, hidden)
+        self.scales = self.buf[offs[1]:offs[1] + sizes[1]].view(self.scale_rows, hidden // 32)
+        self.meta = self.buf[offs[2]:offs[2] + sizes[2]].view(torch.int32).view(self.capacity, 2)
+        self.pairs = self.buf[offs[3]:offs[3] + sizes[3]].view(dtype).view(tokens * topk, hidden)
+        table = lambda k: (ctypes.c_void_p * self.world)(*[int(p) + offs[k] for p in self.hdl.buffer_ptrs])
+        self._peer_codes, self._peer_scales, self._peer_meta, self._peer_pairs, self._peer_flags = (
+            table(k) for k in range(5))
+        self._lib = _cabi.load()
+        self._check = _cabi.check
+        self._dtype_code = _cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16
+        self.work = {}
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)          # every rank's buffers (and flags) are zeroed before anyone stores
+
+    def barrier(self, device):
+        """Stream-ordered barrier of the ranks (bounded wait on the device; see es_b200_ep_barrier)."""
+        self._check(self._lib.es_b200_ep_barrier(self._peer_flags, self.rank, self.world,
+                                                 torch.cuda.current_stream(device).cuda_stream))
+
+    def plan(self, topk_ids: torch.Tensor) -> dict:
+        flat = topk_ids.reshape(-1).to(torch.int64)
+        counts = torch.zeros(self.num_experts, dtype=torch.int64, device=flat.device)
+        counts.scatter_add_(0, flat, torch.ones_like(flat))
+        counts_all = torch.empty((self.world, self.num_experts), dtype=torch.int64, device=flat.device)
+        dist.all_gather_into_tensor(counts_all, counts, group=self.group)      # the one collective of the layer
+        return routing_tables(topk_ids, counts_all, self.rank, self.hidden)
+
+    def dispatch(self, x: torch.Tensor, plan: dict):
+        """x [tokens, H] -> (codes [capacity, H] e4m3, swizzled scales) of the rows routed to my experts."""
+        assert x.shape == (self.tokens, self.hidden) and x.dtype == self.dtype and x.is_contiguous()
+        s = torch.cuda.current_stream(x.device).cuda_stream
+        self._check(self._lib.es_b200_ep_dispatch_quant_push(
+            x.data_ptr(), self._dtype_code, plan["dst_rank"].data_ptr(), plan["dst_row"].data_ptr(),
+            plan["dst_scale_offset"].data_ptr(), self._peer_codes, self._peer_scales, self._peer_meta, self.rank,
+            self.world, self.tokens, self.topk, self.hidden, self.capacity, self.scale_bytes, s))
+        self.barrier(x.device)                  # all ranks' stores into my buffers are complete and visible
+        return self.codes, self.scales
+
+    def combine(self, y: torch.Tensor, plan: dict, topk_weights: torch.Tensor) -> torch.Tensor:
+        """y [capacity, H] expert outputs in receive order -> [tokens, H] = sum_j w[token, j] * y(token, j)."""
+        assert y.shape == (self.capacity, self.hidden) and y.dtype == self.dtype and y.is_contiguous()
+        s = torch.cuda.current_stream(y.device).cuda_stream
+        self._check(self._lib.es_b200_ep_combine_push(
+            y.data_ptr(), self.meta.data_ptr(), plan["total_rows"].data_ptr(), self._peer_pairs, self.world,
+            self.capacity, self.tokens * self.topk, self.hidden, 2, s))
+        self.barrier(y.device)
+        out = torch.empty((self.tokens, self.hidden), dtype=self.dtype, device=y.device)
+        w = topk_weights.to(torch.float32).contiguous()
+        self._check(self._lib.es_b200_ep_topk_weighted_sum(self.pairs.data_ptr(), self._dtype_code, w.data_ptr(),
+                                                           out.data_ptr(), self.tokens, self.topk, self.hidden, s))
+        return out
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                shard: ExpertShard) -> torch.Tensor:
+        plan = self.plan(topk_ids)
+        a, sfa = self.dispatch(x, plan)
+        y = shard.forward_codes(a, sfa, plan["rows"], plan["expert_offsets"], plan["blockscale_offsets"], self.work)
+        return self.combine(y, plan, topk_weights)

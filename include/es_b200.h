@@ -121,6 +121,41 @@ int es_b200_fp8_blockwise_grouped_mm(const void* a, const void* b, const float* 
                                      void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * Expert-parallel exchange over peer memory (one process per GPU; the experts of a layer are spread over the GPUs of a
+ * node).  No counterpart in the reference, which has no distributed code: these three calls replace what a caller
+ * would otherwise build from an all-to-all, a permutation and es_sm100_mxfp8_blockscaled_grouped_quant
+ * (ops.py:40-50) on the way in, and an all-to-all plus a weighted sum on the way out.  The peer_* arrays are HOST
+ * arrays of `world` device pointers, entry i being GPU i's buffer mapped into this process (peer access enabled;
+ * entry my_rank is the local buffer).  The calls only enqueue plain stores to those buffers; the caller orders the
+ * GPUs with a barrier after each step.  Destinations out of range are skipped and reported by es_b200_check_status.
+ *
+ * es_b200_ep_dispatch_quant_push: quantises each of the `tokens` rows of x [tokens, k] once (MXFP8, bit-identical to
+ *   the grouped quant) and stores, for each of its topk destinations j (pair = token * topk + j): the codes to row
+ *   dst_row[pair] of peer_codes[dst_rank[pair]] ([capacity_rows, k] bytes), the row's scale words to
+ *   peer_scales[dst_rank[pair]] + dst_scale_offset[pair] + 512 * (K tile) (dst_scale_offset = byte offset of the row's
+ *   word for K tile 0 in the swizzled layout, i.e. blockscale_offset * k/32 + the row's position inside its expert),
+ *   and (my_rank, pair) to row dst_row[pair] of peer_meta[dst_rank[pair]] ([capacity_rows, 2] int32).
+ * es_b200_ep_combine_push: stores row r < *num_rows_dev of y [capacity_rows, n] (2-byte elements) to row meta[r][1]
+ *   of peer_pairs[meta[r][0]] ([pairs_per_rank, n]).
+ * es_b200_ep_topk_weighted_sum: out[t, :] = sum_j weights[t, j] * pairs[t * topk + j, :] (fp32 accumulation in j order).
+ * es_b200_ep_barrier: every GPU calls it the same number of times; peer_flags[i] is GPU i's flag array (17 uint32,
+ *   zeroed once before first use).  One 32-thread kernel announces this GPU's next epoch in every peer's array and
+ *   waits until all peers have announced theirs (at most five seconds, then it sets a status bit and returns).  Work
+ *   enqueued after it on `stream` sees everything the peers stored to this GPU before their matching call.
+ */
+int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const int32_t* dst_rank, const int32_t* dst_row,
+                                   const int64_t* dst_scale_offset, const void* const* peer_codes,
+                                   const void* const* peer_scales, const void* const* peer_meta, int my_rank,
+                                   int world, int tokens, int topk, int k, int64_t capacity_rows, int64_t scale_bytes,
+                                   void* stream);
+int es_b200_ep_combine_push(const void* y, const int32_t* meta, const int32_t* num_rows_dev,
+                            const void* const* peer_pairs, int world, int64_t capacity_rows, int64_t pairs_per_rank,
+                            int n, int elem_bytes, void* stream);
+int es_b200_ep_topk_weighted_sum(const void* pairs, int dtype, const float* weights, void* out, int tokens, int topk,
+                                 int n, void* stream);
+int es_b200_ep_barrier(const void* const* peer_flags, int my_rank, int world, void* stream);
+
+/*
  * Device-side status word of the grouped GEMMs.  Every wait inside the kernels is bounded; a wait that gives up
  * sets a bit in a library-owned device word and the kernel exits cleanly.  This call synchronises `stream`, copies
  * that word to the host, clears it, and returns ES_B200_OK or ES_B200_ERR_DEVICE_TIMEOUT.  Optional: intended for

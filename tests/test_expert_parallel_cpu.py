@@ -82,3 +82,48 @@ def test_silu_mul():
     g = torch.randn(5, 8)
     out = silu_mul(g)
     assert torch.allclose(out, torch.nn.functional.silu(g[:, :4]) * g[:, 4:], atol=1e-6)
+
+
+@pytest.mark.parametrize("world,num_experts,topk,tokens", [(2, 8, 2, 37), (4, 16, 4, 21), (8, 128, 8, 64)])
+def test_routing_tables_of_the_fused_exchange(world, num_experts, topk, tokens):
+    """routing_tables (the address arithmetic of the peer-memory dispatch) for every rank of a simulated job: the
+    destinations of all ranks tile each owner's receive buffer exactly, rows of one expert are contiguous and ordered
+    by (source rank, token, j) — the order the all-to-all path delivers — and the scale offsets are the swizzled
+    positions of those rows."""
+    from expert_specialization_moe_b200.expert_parallel import routing_tables
+    hidden = 256
+    g = torch.Generator().manual_seed(world * 100 + topk)
+    ids = [torch.stack([torch.randperm(num_experts, generator=g)[:topk] for _ in range(tokens)]) for _ in range(world)]
+    counts_all = torch.stack([torch.bincount(i.reshape(-1), minlength=num_experts) for i in ids])
+    tabs = [routing_tables(ids[r], counts_all, r, hidden) for r in range(world)]
+    e_local = num_experts // world
+    kt = hidden // 128
+    for d in range(world):
+        total = int(tabs[d]["total_rows"])
+        # expected arrival order on owner d: expert-major, then source rank, then the source's (token, j) order
+        expected = []
+        for e in range(d * e_local, (d + 1) * e_local):
+            for s in range(world):
+                flat = ids[s].reshape(-1)
+                expected += [(s, int(p)) for p in torch.nonzero(flat == e).reshape(-1)]
+        assert len(expected) == total
+        got = [None] * total
+        for s in range(world):
+            t = tabs[s]
+            for p in torch.nonzero(t["dst_rank"] == d).reshape(-1).tolist():
+                row = int(t["dst_row"][p])
+                assert 0 <= row < total and got[row] is None
+                got[row] = (s, p)
+                # scale offset of the row: expert's blockscale offset + swizzled position inside the expert
+                e = int(ids[s].reshape(-1)[p])
+                le = e - d * e_local
+                r_local = row - int(tabs[d]["expert_offsets"][le])
+                want = (int(tabs[d]["blockscale_offsets"][le]) * (hidden // 32) + (r_local // 128) * kt * 512
+                        + (r_local % 32) * 16 + ((r_local % 128) // 32) * 4)
+                assert int(t["dst_scale_offset"][p]) == want
+        assert got == expected
+        rows = tabs[d]["rows"].to(torch.int64)
+        assert int(rows.sum()) == total
+        assert torch.equal(tabs[d]["expert_offsets"].to(torch.int64), torch.cumsum(rows, 0) - rows)
+        mp128 = (rows + 127) // 128 * 128
+        assert torch.equal(tabs[d]["blockscale_offsets"].to(torch.int64), torch.cumsum(mp128, 0) - mp128)

@@ -56,6 +56,92 @@ def _worker(rank, world, port, q):
         q.put((rank, None, traceback.format_exc()))
 
 
+def _worker_fused(rank, world, port, q):
+    """Fused exchange (peer-memory dispatch / combine) against the all-to-all path on the same inputs."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        from expert_specialization_moe_b200 import expert_parallel as ep
+        from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
+        from expert_specialization_moe_b200 import _cabi
+        import ctypes
+
+        E, topk, H, I, tokens = 8, 2, 256, 128, 300
+        dev = torch.device("cuda", rank)
+        gw = torch.Generator(device=dev).manual_seed(1)
+        w1 = (torch.randn((E, 2 * I, H), generator=gw, device=dev) * 0.05).to(torch.bfloat16)
+        w2 = (torch.randn((E, H, I), generator=gw, device=dev) * 0.05).to(torch.bfloat16)
+        e_local = E // world
+        shard = ep.ExpertShard(w1[rank * e_local:(rank + 1) * e_local].contiguous(),
+                               w2[rank * e_local:(rank + 1) * e_local].contiguous())
+        fx = ep.FusedExchange(E, topk, tokens, H, dev)
+        worst = 0.0
+        for it in range(3):                       # several rounds: the receive buffers and flags are reused
+            g = torch.Generator(device=dev).manual_seed(10 + rank + 100 * it)
+            x = torch.randn((tokens, H), generator=g, device=dev).to(torch.bfloat16)
+            p = torch.softmax(torch.randn((tokens, E), generator=g, device=dev), -1)
+            wts, ids = torch.topk(p, topk, dim=-1)
+            wts = wts / wts.sum(-1, keepdim=True)
+            # all-to-all path
+            plan = ep.make_plan(ids, E)
+            rows = ep.dispatch(x, plan)
+            ps, eo, bo, sf_rows = plan.problem_tensors(2 * I, H)
+            a_ref = torch.empty((rows.shape[0], H), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+            sf_ref = torch.zeros((max(sf_rows, 128), H // 32), dtype=torch.uint8, device=dev)
+            quant(rows, ps, eo, bo, a_ref, sf_ref)
+            out_ref = ep.combine(shard.forward(rows, plan), plan, wts)
+            # fused path
+            fplan = fx.plan(ids)
+            a, sfa = fx.dispatch(x, fplan)
+            torch.cuda.synchronize()
+            n = rows.shape[0]
+            assert int(fplan["total_rows"]) == n
+            assert torch.equal(fplan["expert_offsets"], eo) and torch.equal(fplan["blockscale_offsets"], bo)
+            assert torch.equal(a[:n].view(torch.uint8), a_ref.view(torch.uint8)), "dispatched codes differ"
+            # scale bytes of valid rows: compare through the row -> offset map of the swizzled layout
+            kt = H // 128
+            counts = fplan["rows"].tolist()
+            for le, m in enumerate(counts):
+                r = torch.arange(m, device=dev)
+                base = int(bo[le]) * (H // 32) + (r // 128) * kt * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4
+                idx = (base.unsqueeze(1) + torch.arange(kt, device=dev).unsqueeze(0) * 512).unsqueeze(2) \
+                    + torch.arange(4, device=dev).view(1, 1, 4)
+                assert torch.equal(sfa.reshape(-1)[idx], sf_ref.reshape(-1)[idx]), f"scales of local expert {le} differ"
+            out = fx.forward(x, ids, wts, shard)
+            torch.cuda.synchronize()
+            worst = max(worst, float((out.float() - out_ref.float()).abs().max()
+                                     / out_ref.float().abs().max().clamp_min(1e-6)))
+        raw = ctypes.c_uint32(0)
+        rc = _cabi.load().es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
+        q.put((rank, worst if rc == 0 else float("inf"), None))
+        dist.destroy_process_group()
+    except Exception:
+        import traceback
+        q.put((rank, None, traceback.format_exc()))
+
+
+def test_two_gpu_fused_exchange():
+    """Peer-memory dispatch (quantise once, push codes + scales + return address) and combine against the all-to-all
+    path: dispatched codes and scales bit-identical, layer output equal up to the summation order of the top-k rows."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_fused, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, err, tb in res:
+        assert tb is None, f"rank {rank}:\n{tb}"
+        assert err < 1e-2, f"rank {rank}: relative max difference {err}"
+
+
 def test_two_gpu_moe_layer():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
