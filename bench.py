@@ -47,7 +47,10 @@ WORKLOADS = {
     # grouped MXFP8 quantisation alone (N is unused): bf16 N(0,1) with 1% outliers x50
     "quant": (256, 32768, 0, 7168, "grouped MXFP8 quantisation: bf16 [32768, 7168], E=256, Zipf(1.2) counts, "
                                    "e4m3 codes + swizzled UE8M0 scales"),
-    "qwen3_ep": (128, 0, 0, 0, "Qwen3-30B-A3B-shaped MoE layer with expert parallelism (N >= 2)"),
+    "qwen3_ep": (128, 0, 0, 0, "Qwen3-30B-A3B-shaped MoE layer with expert parallelism (N >= 2), dispatch / combine "
+                               "over peer memory (FusedExchange)"),
+    "qwen3_ep_nccl": (128, 0, 0, 0, "Qwen3-30B-A3B-shaped MoE layer with expert parallelism (N >= 2), NCCL all-to-all "
+                                    "dispatch / combine"),
     # the reference's own published benchmark (benchmark/benchmark_es_fp8_blockwise_moe.py: uniform-random top-8
     # routing, bf16 output), FP8-blockwise op; T = batch x top-8.  H200 numbers of the reference for these two points:
     # 264.8 us = 113.6 TFLOP/s and 187.2 us = 80.3 TFLOP/s (media/performance_data/H200_bench.log:14-16, 62-64)
@@ -286,7 +289,14 @@ def bench_ep_layer(args, device, rank, world, dist):
     p = torch.softmax(torch.randn((tokens, E), generator=g, device=device), -1)
     wts, ids = torch.topk(p, topk, dim=-1)
     wts = (wts / wts.sum(-1, keepdim=True)).to(torch.float32)
-    step = lambda: ep.moe_forward(x, ids, wts, E, shard.forward)
+    fused = args.workload == "qwen3_ep"
+    if fused:
+        # capacity: 2x the balanced share is ample for softmax-of-N(0,1) routing; overflow would be reported as an
+        # out-of-range destination by es_b200_check_status below
+        fx = ep.FusedExchange(E, topk, tokens, H, device, capacity_rows=2 * tokens * topk)
+        step = lambda: fx.forward(x, ids, wts, shard)
+    else:
+        step = lambda: ep.moe_forward(x, ids, wts, E, shard.forward)
 
     def barrier():
         dist.barrier()
@@ -308,6 +318,13 @@ def bench_ep_layer(args, device, rank, world, dist):
     clocks = sampler.stop() if rank == 0 else None
     ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=device)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    import ctypes
+    from expert_specialization_moe_b200 import _cabi
+    raw = ctypes.c_uint32(0)
+    _cabi.load().es_b200_check_status(torch.cuda.current_stream(device).cuda_stream, ctypes.byref(raw))
+    st = torch.tensor([int(raw.value)], dtype=torch.int64, device=device)
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    status = int(st[0])
     if rank == 0:
         flops = 2.0 * tokens * topk * world * (2 * I * H + H * I)
         line = {"metric": "MoE layer (expert parallel) grouped-GEMM TFLOPS incl. dispatch/combine",
@@ -315,8 +332,13 @@ def bench_ep_layer(args, device, rank, world, dist):
                 "warmup": args.warmup, "ms_per_step": float(ms[0]), "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "mxfp8_e4m3", "data": "synthetic",
                 "config": {"workload": "Qwen3-30B-A3B-shaped MoE layer: E=128, top-8, hidden 2048, intermediate 768, "
-                                       "16384 tokens per GPU, NCCL all-to-all dispatch/combine", "experts_per_gpu": e_local},
-                "clocks": clocks, "gpu_launches": args.steps * 7}
+                                       "16384 tokens per GPU, " + ("dispatch/combine as peer-memory stores fused with "
+                                       "the quantisation (FusedExchange)" if fused else "NCCL all-to-all dispatch/combine"),
+                           "experts_per_gpu": e_local},
+                "clocks": clocks, "device_status": status,
+                # ours per step: dispatch-quant-push, 2 barriers, up to 3 + 3 GEMM bucket kernels, silu-quant,
+                # combine-push, weighted sum (fused) / 2 quant kernels + GEMMs (all-to-all path)
+                "gpu_launches": args.steps * (12 if fused else 8)}
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()
@@ -561,7 +583,7 @@ def main():
 
     if args.workload.startswith("quant"):
         return bench_quant(args, E, T, K, desc, device, rank, world, dist)
-    if args.workload == "qwen3_ep":
+    if args.workload.startswith("qwen3_ep"):
         return bench_ep_layer(args, device, rank, world, dist)
     if args.workload.startswith("blockwise"):
         return bench_blockwise(args, E, T, N, K, desc, device, rank, world, dist)

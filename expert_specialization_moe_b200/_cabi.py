@@ -50,6 +50,13 @@ def _declare(lib):
     lib.es_b200_ep_topk_weighted_sum.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
     lib.es_b200_ep_barrier.restype = c_int
     lib.es_b200_ep_barrier.argtypes = [POINTER(c_void_p), c_int, c_int, c_void_p]
+    lib.es_b200_ep_route_count.restype = c_int
+    lib.es_b200_ep_route_count.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, POINTER(c_void_p), c_int,
+                                           c_int, c_void_p]
+    lib.es_b200_ep_route_tables.restype = c_int
+    lib.es_b200_ep_route_tables.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p]
     lib.es_b200_check_status.restype = c_int
     lib.es_b200_check_status.argtypes = [c_void_p, POINTER(c_uint32)]
 

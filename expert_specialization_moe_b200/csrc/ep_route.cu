@@ -1,0 +1,212 @@
+// Routing tables of the expert-parallel exchange, computed on the device in three small launches:
+//
+//   es_b200_ep_route_count   per-segment histograms of this GPU's (token, j) pairs over the experts, their exclusive
+//                            prefix over the segments, and this GPU's per-expert totals stored into every peer's
+//                            copy of the count matrix counts_all [world, E]            (barrier between the two calls)
+//   es_b200_ep_route_tables  from counts_all: rows / offsets of this GPU's experts, and for each of its own pairs the
+//                            owner GPU, the row in the owner's receive buffer and the byte offset of the row's scale
+//                            words (swizzled layout) — the inputs of es_b200_ep_dispatch_quant_push.
+//
+// Order on the owner: expert-major, inside an expert by source GPU, inside a source by pair index (token-major) — what
+// a stable sort by expert followed by an all-to-all delivers.  A pair's rank among its GPU's pairs to the same expert
+// is found without sorting: the pairs are cut into 256 contiguous segments, one warp walks one segment 32 pairs at a
+// time (match_any gives the rank inside the step, a per-warp running count per expert the rank before it).
+#include "common.cuh"
+#include "mxfp8_quant_math.cuh"
+
+namespace es_b200 {
+namespace route {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int BLOCKS = 32;
+constexpr int SEGMENTS = BLOCKS * WARPS;       // 256
+constexpr int MAX_WORLD = 16;
+
+struct PeerTable {
+  void* ptr[MAX_WORLD];
+};
+
+__device__ __forceinline__ int load_id(const void* ids, int ids_int64, int i) {
+  return ids_int64 ? (int)static_cast<const long long*>(ids)[i] : static_cast<const int*>(ids)[i];
+}
+
+__device__ __forceinline__ int segment_len(int pairs) {       // pairs per segment, a multiple of 32
+  return ((pairs + SEGMENTS - 1) / SEGMENTS + 31) & ~31;
+}
+
+// seg_counts[seg][e] = number of pairs of segment seg routed to expert e (ids outside [0, E) are not counted)
+__global__ void __launch_bounds__(THREADS)
+count_kernel(const void* __restrict__ ids, int ids_int64, int pairs, int num_experts, int* __restrict__ seg_counts) {
+  extern __shared__ int hist[];                 // [WARPS][E]
+  pdl_wait_prior_grid();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int* mine = hist + warp * num_experts;
+  for (int e = lane; e < num_experts; e += 32) mine[e] = 0;
+  __syncwarp();
+  const int seg = blockIdx.x * WARPS + warp;
+  const int len = segment_len(pairs);
+  const int begin = seg * len;
+  const int end = min(begin + len, pairs);
+  for (int i = begin + lane; i < end; i += 32) {
+    const int e = load_id(ids, ids_int64, i);
+    if (e >= 0 && e < num_experts) atomicAdd(&mine[e], 1);
+  }
+  __syncwarp();
+  for (int e = lane; e < num_experts; e += 32) seg_counts[(int64_t)seg * num_experts + e] = mine[e];
+}
+
+// seg_base[seg][e] = pairs to expert e in segments before seg; this GPU's totals go to row my_rank of every peer's
+// count matrix
+__global__ void __launch_bounds__(1024)
+publish_kernel(const int* __restrict__ seg_counts, int* __restrict__ seg_base, int num_experts,
+               const __grid_constant__ PeerTable counts_all, int my_rank, int world) {
+  pdl_wait_prior_grid();
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
+    int running = 0;
+#pragma unroll 8
+    for (int s = 0; s < SEGMENTS; ++s) {
+      const int c = seg_counts[(int64_t)s * num_experts + e];
+      seg_base[(int64_t)s * num_experts + e] = running;
+      running += c;
+    }
+    for (int p = 0; p < world; ++p) static_cast<int*>(counts_all.ptr[p])[my_rank * num_experts + e] = running;
+  }
+  __threadfence_system();
+}
+
+__global__ void __launch_bounds__(THREADS)
+tables_kernel(const void* __restrict__ ids, int ids_int64, int pairs, int num_experts, const int* __restrict__ seg_base,
+              const int* __restrict__ counts_all, int my_rank, int world, int k, int* __restrict__ dst_rank,
+              int* __restrict__ dst_row, long long* __restrict__ dst_scale_offset, int* __restrict__ rows_out,
+              int* __restrict__ eo_out, int* __restrict__ bo_out, int* __restrict__ total_rows_out) {
+  // shared: row_base[E] (row of the expert's first row from THIS GPU in the owner's buffer), sc_base[E] (scale-row
+  // offset of the expert on its owner), in_expert[E] (rows of lower-ranked GPUs inside the expert), run[WARPS][E]
+  extern __shared__ int sh[];
+  int* eo_s = sh;
+  int* bo_s = sh + num_experts;
+  int* before_s = sh + 2 * num_experts;
+  int* run = sh + 3 * num_experts;
+  pdl_wait_prior_grid();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e_local = num_experts / world;
+  // per-expert totals; each owner's experts are then scanned serially by one thread (E / world entries: short)
+  for (int e = threadIdx.x; e < num_experts; e += THREADS) {
+    int m = 0, before = 0;
+    for (int s = 0; s < world; ++s) {
+      const int c = counts_all[s * num_experts + e];
+      if (s < my_rank) before += c;
+      m += c;
+    }
+    eo_s[e] = m;            // totals for now
+    before_s[e] = before;
+  }
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const int d = threadIdx.x;
+    int rows = 0, srows = 0;
+    for (int le = 0; le < e_local; ++le) {
+      const int e = d * e_local + le;
+      const int m = eo_s[e];
+      eo_s[e] = rows;
+      bo_s[e] = srows;
+      if (d == my_rank && blockIdx.x == 0) {
+        rows_out[le] = m;
+        eo_out[le] = rows;
+        bo_out[le] = srows;
+      }
+      rows += m;
+      srows += (m + 127) & ~127;
+    }
+    if (d == my_rank && blockIdx.x == 0) *total_rows_out = rows;
+  }
+  const int seg = blockIdx.x * WARPS + warp;
+  int* my_run = run + warp * num_experts;
+  for (int e = lane; e < num_experts; e += 32) my_run[e] = seg_base[(int64_t)seg * num_experts + e];
+  __syncthreads();
+
+  const int kt = k >> 7;
+  const long long sf_row_bytes = k >> 5;
+  const int len = segment_len(pairs);
+  const int begin = seg * len;
+  const int end = min(begin + len, pairs);
+  for (int i0 = begin; i0 < end; i0 += 32) {
+    const int i = i0 + lane;
+    int e = i < end ? load_id(ids, ids_int64, i) : -1;
+    if (e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_step = __popc(peers & ((1u << lane) - 1u));
+    int pos = 0;
+    if (e >= 0) pos = my_run[e] + rank_in_step;
+    __syncwarp();
+    if (e >= 0 && rank_in_step == 0) my_run[e] += __popc(peers);
+    __syncwarp();
+    if (i < end) {
+      if (e >= 0) {
+        const int r_local = before_s[e] + pos;                 // row inside the expert, on the owner
+        dst_rank[i] = e / e_local;
+        dst_row[i] = eo_s[e] + r_local;
+        dst_scale_offset[i] = (long long)bo_s[e] * sf_row_bytes + scale_word_offset(r_local, kt);
+      } else {
+        dst_rank[i] = -1;                                       // reported and skipped by the dispatch kernel
+        dst_row[i] = 0;
+        dst_scale_offset[i] = 0;
+      }
+    }
+  }
+}
+
+}  // namespace route
+}  // namespace es_b200
+
+extern "C" int es_b200_ep_route_count(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
+                                      int32_t* segment_counts, int32_t* segment_base,
+                                      const void* const* peer_counts_all, int my_rank, int world, void* stream) {
+  using namespace es_b200;
+  ES_REQUIRE(world >= 1 && world <= route::MAX_WORLD, "world size must be in [1, %d]", route::MAX_WORLD);
+  ES_REQUIRE(my_rank >= 0 && my_rank < world, "rank out of range");
+  ES_REQUIRE(num_experts >= 1 && num_experts <= ES_B200_MAX_EXPERTS && num_experts % world == 0,
+             "num_experts must be a multiple of the world size and at most %d", ES_B200_MAX_EXPERTS);
+  ES_REQUIRE(pairs >= 0, "pairs out of range");
+  ES_REQUIRE(topk_ids && segment_counts && segment_base && peer_counts_all, "null pointer argument");
+  route::PeerTable table;
+  for (int i = 0; i < route::MAX_WORLD; ++i) table.ptr[i] = nullptr;
+  for (int i = 0; i < world; ++i) {
+    ES_REQUIRE(peer_counts_all[i] != nullptr, "peer pointer %d is null", i);
+    table.ptr[i] = const_cast<void*>(peer_counts_all[i]);
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)route::WARPS * num_experts * sizeof(int);
+  route::count_kernel<<<route::BLOCKS, route::THREADS, smem, s>>>(topk_ids, ids_are_int64, pairs, num_experts,
+                                                                  segment_counts);
+  ES_CUDA_TRY(cudaGetLastError());
+  route::publish_kernel<<<1, 1024, 0, s>>>(segment_counts, segment_base, num_experts, table, my_rank, world);
+  ES_CUDA_TRY(cudaGetLastError());
+  return ES_B200_OK;
+}
+
+extern "C" int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
+                                       const int32_t* segment_base, const int32_t* counts_all, int my_rank, int world,
+                                       int k, int32_t* dst_rank, int32_t* dst_row, int64_t* dst_scale_offset,
+                                       int32_t* rows, int32_t* expert_offsets, int32_t* blockscale_offsets,
+                                       int32_t* total_rows, void* stream) {
+  using namespace es_b200;
+  ES_REQUIRE(world >= 1 && world <= route::MAX_WORLD, "world size must be in [1, %d]", route::MAX_WORLD);
+  ES_REQUIRE(my_rank >= 0 && my_rank < world, "rank out of range");
+  ES_REQUIRE(num_experts >= 1 && num_experts <= ES_B200_MAX_EXPERTS && num_experts % world == 0,
+             "num_experts must be a multiple of the world size and at most %d", ES_B200_MAX_EXPERTS);
+  ES_REQUIRE(k > 0 && k % 128 == 0, "k must align to 128");
+  ES_REQUIRE(pairs >= 0, "pairs out of range");
+  ES_REQUIRE(topk_ids && segment_base && counts_all && dst_rank && dst_row && dst_scale_offset && rows &&
+                 expert_offsets && blockscale_offsets && total_rows,
+             "null pointer argument");
+  const size_t smem = (size_t)(3 + route::WARPS) * num_experts * sizeof(int);
+  route::tables_kernel<<<route::BLOCKS, route::THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
+      topk_ids, ids_are_int64, pairs, num_experts, segment_base, counts_all, my_rank, world, k, dst_rank, dst_row,
+      reinterpret_cast<long long*>(dst_scale_offset), rows, expert_offsets, blockscale_offsets, total_rows);
+  ES_CUDA_TRY(cudaGetLastError());
+  return ES_B200_OK;
+}

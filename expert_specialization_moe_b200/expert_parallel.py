@@ -14,8 +14,8 @@ Expert e lives on rank e // (E / G) (contiguous shards), local index e % (E / G)
 
 `FusedExchange` is the same layer without the all-to-alls: every rank quantises its tokens once and stores codes,
 scales and return addresses straight into the owners' receive buffers over NVLink (peer-mapped symmetric memory),
-the expert outputs are stored straight back into the senders' (token, j) slots, and the only collective left is an
-all-gather of the per-expert counts.  Nothing in it needs a size on the host, so a layer is a fixed sequence of launches.
+the expert outputs are stored straight back into the senders' (token, j) slots, and the per-expert counts travel the
+same way.  Nothing in it needs a size on the host, so a layer is a fixed sequence of launches.
 """
 from __future__ import annotations
 
@@ -263,7 +263,8 @@ class FusedExchange:
         self.capacity = int(capacity_rows or self.world * tokens * topk)
         self.scale_rows = (self.capacity + 128 * self.e_local + 127) // 128 * 128
         self.scale_bytes = self.scale_rows * (hidden // 32)
-        sizes = [self.capacity * hidden, self.scale_bytes, self.capacity * 8, tokens * topk * hidden * 2, 17 * 4]
+        sizes = [self.capacity * hidden, self.scale_bytes, self.capacity * 8, tokens * topk * hidden * 2, 17 * 4,
+                 self.world * num_experts * 4]
         offs, total = [], 0
         for sz in sizes:
             offs.append(total)
@@ -276,8 +277,16 @@ class FusedExchange:
         self.meta = self.buf[offs[2]:offs[2] + sizes[2]].view(torch.int32).view(self.capacity, 2)
         self.pairs = self.buf[offs[3]:offs[3] + sizes[3]].view(dtype).view(tokens * topk, hidden)
         table = lambda k: (ctypes.c_void_p * self.world)(*[int(p) + offs[k] for p in self.hdl.buffer_ptrs])
-        self._peer_codes, self._peer_scales, self._peer_meta, self._peer_pairs, self._peer_flags = (
-            table(k) for k in range(5))
+        (self._peer_codes, self._peer_scales, self._peer_meta, self._peer_pairs, self._peer_flags,
+         self._peer_counts) = (table(k) for k in range(6))
+        self.counts_all = self.buf[offs[5]:offs[5] + sizes[5]].view(torch.int32).view(self.world, num_experts)
+        pairs = tokens * topk
+        i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=device)
+        self._seg_counts, self._seg_base = i32(256, num_experts), i32(256, num_experts)
+        self._tables = {"dst_rank": i32(pairs), "dst_row": i32(pairs),
+                        "dst_scale_offset": torch.empty(pairs, dtype=torch.int64, device=device),
+                        "rows": i32(self.e_local), "expert_offsets": i32(self.e_local),
+                        "blockscale_offsets": i32(self.e_local), "total_rows": i32(1)}
         self._lib = _cabi.load()
         self._check = _cabi.check
         self._dtype_code = _cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16
@@ -291,12 +300,25 @@ class FusedExchange:
                                                  torch.cuda.current_stream(device).cuda_stream))
 
     def plan(self, topk_ids: torch.Tensor) -> dict:
-        flat = topk_ids.reshape(-1).to(torch.int64)
-        counts = torch.zeros(self.num_experts, dtype=torch.int64, device=flat.device)
-        counts.scatter_add_(0, flat, torch.ones_like(flat))
-        counts_all = torch.empty((self.world, self.num_experts), dtype=torch.int64, device=flat.device)
-        dist.all_gather_into_tensor(counts_all, counts, group=self.group)      # the one collective of the layer
-        return routing_tables(topk_ids, counts_all, self.rank, self.hidden)
+        """Routing tables of this step (three small launches and a barrier; the returned tensors are reused by the
+        next call).  `routing_tables` is the same arithmetic in torch."""
+        assert topk_ids.shape == (self.tokens, self.topk) and topk_ids.is_contiguous()
+        assert topk_ids.dtype in (torch.int32, torch.int64)
+        dev = topk_ids.device
+        s = torch.cuda.current_stream(dev).cuda_stream
+        is64 = 1 if topk_ids.dtype == torch.int64 else 0
+        pairs = self.tokens * self.topk
+        t = self._tables
+        self._check(self._lib.es_b200_ep_route_count(topk_ids.data_ptr(), is64, pairs, self.num_experts,
+                                                     self._seg_counts.data_ptr(), self._seg_base.data_ptr(),
+                                                     self._peer_counts, self.rank, self.world, s))
+        self.barrier(dev)                       # every rank's counts have arrived in my count matrix
+        self._check(self._lib.es_b200_ep_route_tables(
+            topk_ids.data_ptr(), is64, pairs, self.num_experts, self._seg_base.data_ptr(), self.counts_all.data_ptr(),
+            self.rank, self.world, self.hidden, t["dst_rank"].data_ptr(), t["dst_row"].data_ptr(),
+            t["dst_scale_offset"].data_ptr(), t["rows"].data_ptr(), t["expert_offsets"].data_ptr(),
+            t["blockscale_offsets"].data_ptr(), t["total_rows"].data_ptr(), s))
+        return t
 
     def dispatch(self, x: torch.Tensor, plan: dict):
         """x [tokens, H] -> (codes [capacity, H] e4m3, swizzled scales) of the rows routed to my experts."""

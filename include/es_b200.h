@@ -156,6 +156,27 @@ int es_b200_ep_topk_weighted_sum(const void* pairs, int dtype, const float* weig
 int es_b200_ep_barrier(const void* const* peer_flags, int my_rank, int world, void* stream);
 
 /*
+ * Routing tables of the exchange, on the device (no counterpart in the reference).  topk_ids holds this GPU's
+ * `pairs` = tokens * topk expert ids (int32, or int64 when ids_are_int64), token-major.
+ * es_b200_ep_route_count: histograms the ids (scratch: segment_counts and segment_base, 256 * num_experts int32 each)
+ *   and stores this GPU's per-expert totals into row my_rank of every peer's count matrix peer_counts_all[i]
+ *   ([world, num_experts] int32).  Then es_b200_ep_barrier, then
+ * es_b200_ep_route_tables: reads the local count matrix and writes, for each pair, the owner GPU (expert / (E/world)),
+ *   the row in the owner's receive buffer and the byte offset of the row's scale words (the three per-pair inputs of
+ *   es_b200_ep_dispatch_quant_push; an id outside [0, E) gives owner -1, which that call reports and skips), and for
+ *   this GPU's own experts: rows[e], expert_offsets[e], blockscale_offsets[e] (E/world entries each) and total_rows[0]
+ *   — the problem description of the grouped GEMMs that follow.  On the owner, rows are ordered by expert, then
+ *   source GPU, then pair index.
+ */
+int es_b200_ep_route_count(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
+                           int32_t* segment_counts, int32_t* segment_base, const void* const* peer_counts_all,
+                           int my_rank, int world, void* stream);
+int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
+                            const int32_t* segment_base, const int32_t* counts_all, int my_rank, int world, int k,
+                            int32_t* dst_rank, int32_t* dst_row, int64_t* dst_scale_offset, int32_t* rows,
+                            int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* total_rows, void* stream);
+
+/*
  * Device-side status word of the grouped GEMMs.  Every wait inside the kernels is bounded; a wait that gives up
  * sets a bit in a library-owned device word and the kernel exits cleanly.  This call synchronises `stream`, copies
  * that word to the host, clears it, and returns ES_B200_OK or ES_B200_ERR_DEVICE_TIMEOUT.  Optional: intended for

@@ -94,6 +94,13 @@ def _worker_fused(rank, world, port, q):
             out_ref = ep.combine(shard.forward(rows, plan), plan, wts)
             # fused path
             fplan = fx.plan(ids)
+            # the device-side routing kernels against the same arithmetic in torch
+            cnt = torch.bincount(ids.reshape(-1), minlength=E)
+            cnt_all = torch.empty((world, E), dtype=cnt.dtype, device=dev)
+            dist.all_gather_into_tensor(cnt_all, cnt)
+            want = ep.routing_tables(ids, cnt_all, rank, H)
+            for key, val in want.items():
+                assert torch.equal(fplan[key].to(val.dtype), val), f"routing table {key} differs"
             a, sfa = fx.dispatch(x, fplan)
             torch.cuda.synchronize()
             n = rows.shape[0]
