@@ -35,6 +35,10 @@ def _declare(lib):
     lib.es_b200_mxfp8_grouped_mm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                              c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_void_p,
                                              c_size_t, c_void_p]
+    lib.es_b200_mxfp8_grouped_mm_scatter.restype = c_int
+    lib.es_b200_mxfp8_grouped_mm_scatter.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                     c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_void_p,
+                                                     POINTER(c_void_p), c_int, c_int64, c_void_p]
     lib.es_b200_fp8_blockwise_grouped_mm.restype = c_int
     lib.es_b200_fp8_blockwise_grouped_mm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                      c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p,

@@ -15,6 +15,18 @@ namespace es_b200 {
 
 constexpr int EPI_STAGE_BYTES_PER_WARP = 32 * 32 * 2;
 
+// Optional destination map of the output rows (expert-parallel combine fused into the GEMM): output row r goes to row
+// meta[r].y of the [slots, n] array base[meta[r].x] — another GPU's buffer mapped into this process, or a local one —
+// instead of row r of d.  meta == nullptr: dense output.  Entries out of range are skipped and reported.
+constexpr int SCATTER_MAX_GPUS = 16;
+constexpr uint32_t ERR_SCATTER_DESTINATION = 0x40000u;
+struct RowScatter {
+  const int2* meta;
+  void* base[SCATTER_MAX_GPUS];
+  long long slots;
+  int gpus;
+};
+
 template <typename OutT>
 __device__ __forceinline__ OutT out_from_f32(float v);
 template <>
@@ -26,9 +38,13 @@ __device__ __forceinline__ __half out_from_f32<__half>(float v) { return __float
 // and stores the first `valid` of them: column j goes to dst[j * ld + 0..31] (dst = &d[first token][first n of warp]).
 // `release` is called once, right after the last TMEM read has completed (the accumulator may then be overwritten).
 // TOK = tokens per pass through the shared-memory tile (32: 2 KB per warp; 16: 1 KB per warp, two passes per chunk).
+// With a scatter map, column j goes to the mapped row of output row `first_row + j`, at column offset `col_off`
+// (`dst` is then unused); `status` is the kernel's error word.
 template <typename OutT, int TOK = 32, class Release>
 __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, int valid, OutT* stage_warp, OutT* dst,
-                                                  int64_t ld, bool do_store, int lane, Release release) {
+                                                  int64_t ld, bool do_store, int lane, Release release,
+                                                  const RowScatter& scatter, int64_t first_row, int col_off,
+                                                  uint32_t* status) {
   // two register sets: the TMEM read of chunk c+1 is in flight while chunk c goes through shared memory
   uint32_t va[32], vb[32];
   ptx::tc_ld_32x32b_x32(taddr, va);
@@ -57,7 +73,17 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
             const int tok = it * 8 + (lane >> 2);
             const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
             const int row = c + p * TOK + tok;
-            if (row < valid) *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
+            if (row < valid) {
+              if (scatter.meta == nullptr) {
+                *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
+              } else {
+                const int2 m = scatter.meta[first_row + row];
+                if (m.x >= 0 && m.x < scatter.gpus && m.y >= 0 && m.y < scatter.slots)
+                  *reinterpret_cast<uint4*>(static_cast<OutT*>(scatter.base[m.x]) + (int64_t)m.y * ld + col_off + part * 8) = val;
+                else
+                  atomicOr(status, ERR_SCATTER_DESTINATION);
+              }
+            }
           }
           __syncwarp();
         }

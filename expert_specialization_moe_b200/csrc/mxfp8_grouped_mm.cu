@@ -115,7 +115,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                         const uint8_t* __restrict__ sf_weights, OutT* __restrict__ d,
                         const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
                         const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
-                        int max_rows, int wait_at_start) {
+                        int max_rows, int wait_at_start, const __grid_constant__ RowScatter scatter) {
   constexpr int TOK_TILE = S::TOK_TILE, STAGES = S::STAGES, X_BYTES = S::X_BYTES, STAGE_BYTES = S::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -263,7 +263,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                                 ptx::tc_fence_before_sync();
                                 __syncwarp();
                                 if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
-                              });
+                              }, scatter, ti.row0, ti.nt * TILE_N + q * 32, &g_status);
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
     }
@@ -275,13 +275,14 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     __syncwarp();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (scatter.meta != nullptr) __threadfence_system();   // rows may have gone to other GPUs
   if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
 }
 
 template <typename OutT, class S>
 int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
            const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int min_rows,
-           int max_rows, bool first_of_call, cudaStream_t stream) {
+           int max_rows, bool first_of_call, const RowScatter& scatter, cudaStream_t stream) {
   constexpr int TOK_TILE = S::TOK_TILE;
   constexpr size_t SMEM_BYTES = smem_bytes<S>();
   DeviceInfo info;
@@ -321,7 +322,7 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   cfg.numAttrs = 1;
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sfa, sfb,
                                  static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows, max_rows,
-                                 first_of_call ? 1 : 0));
+                                 first_of_call ? 1 : 0, scatter));
   return ES_B200_OK;
 }
 
@@ -329,9 +330,9 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
 
 namespace mm2 {   // CTA-pair kernel (mxfp8_grouped_mm_pair.cu)
 int launch_bf16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, int, int, cudaStream_t);
+                const int32_t*, int, int64_t, int, int, int64_t, int, int, const RowScatter&, cudaStream_t);
 int launch_fp16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, int, int, cudaStream_t);
+                const int32_t*, int, int64_t, int, int, int64_t, int, int, const RowScatter&, cudaStream_t);
 int read_and_clear_status(uint32_t* out);
 }  // namespace mm2
 namespace ep {    // expert-parallel dispatch / combine kernels (ep_dispatch_combine.cu)
@@ -344,12 +345,11 @@ int read_and_clear_status(uint32_t* out);
 
 extern "C" size_t es_b200_grouped_mm_scratch_bytes(int, int64_t, int, int) { return 0; }
 
-extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d,
-                                        int out_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
-                                        const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n,
-                                        int k, int64_t sfa_rows, void* scratch, size_t scratch_bytes, void* stream) {
-  using namespace es_b200;
-  (void)scratch; (void)scratch_bytes;
+namespace es_b200 {
+static int grouped_mm_impl(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, int out_dtype,
+                           const int32_t* problem_sizes, const int32_t* expert_offsets,
+                           const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n, int k,
+                           int64_t sfa_rows, const RowScatter& scatter, void* stream) {
   ES_REQUIRE(out_dtype == ES_B200_BF16 || out_dtype == ES_B200_FP16, "dtype must be kFloat16 or kBFloat16");
   ES_REQUIRE(k > 0 && k % 128 == 0, "k should align 128");
   ES_REQUIRE(n > 0 && n % 128 == 0, "n should align 128");
@@ -358,7 +358,8 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
   ES_REQUIRE(num_rows >= 0 && num_rows < (int64_t)1 << 31, "num_rows out of range");
   ES_REQUIRE((int64_t)num_experts * n < (int64_t)1 << 31, "num_experts * n out of range");
   if (num_experts == 0 || num_rows == 0) return ES_B200_OK;
-  ES_REQUIRE(a && b && sfa && sfb && d && problem_sizes && expert_offsets && blockscale_offsets, "null pointer argument");
+  ES_REQUIRE(a && b && sfa && sfb && (d || scatter.meta) && problem_sizes && expert_offsets && blockscale_offsets,
+             "null pointer argument");
   ES_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sfa) && aligned16(sfb), "a, b, sfa, sfb must be 16-byte aligned");
   ES_REQUIRE(aligned16(d), "d must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -386,9 +387,9 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
   if (tiny_max >= 1) {
     rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeTiny>(a, b, sfa, sfb, d, problem_sizes, expert_offsets,
                                                          blockscale_offsets, num_experts, num_rows, n, k, 1, tiny_max,
-                                                         first, s)
+                                                         first, scatter, s)
               : mm::launch<__half, mm::ShapeTiny>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets,
-                                                  num_experts, num_rows, n, k, 1, tiny_max, first, s);
+                                                  num_experts, num_rows, n, k, 1, tiny_max, first, scatter, s);
     if (rc != ES_B200_OK) return rc;
     first = false;
   }
@@ -396,18 +397,52 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
   if (heavy_min - 1 > tiny_max && num_rows > tiny_max) {
     rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeMid>(a, b, sfa, sfb, d, problem_sizes, expert_offsets,
                                                         blockscale_offsets, num_experts, num_rows, n, k, tiny_max + 1,
-                                                        heavy_min - 1, first, s)
+                                                        heavy_min - 1, first, scatter, s)
               : mm::launch<__half, mm::ShapeMid>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets,
-                                                 num_experts, num_rows, n, k, tiny_max + 1, heavy_min - 1, first, s);
+                                                 num_experts, num_rows, n, k, tiny_max + 1, heavy_min - 1, first, scatter, s);
     if (rc != ES_B200_OK) return rc;
     first = false;
   }
   if (num_rows < heavy_min) return rc;
   ES_REQUIRE(sfa_rows >= 0, "sfa_rows must be non-negative");
   return bf16 ? mm2::launch_bf16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, s)
+                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, scatter, s)
               : mm2::launch_fp16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, s);
+                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, scatter, s);
+}
+}  // namespace es_b200
+
+extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d,
+                                        int out_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
+                                        const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n,
+                                        int k, int64_t sfa_rows, void* scratch, size_t scratch_bytes, void* stream) {
+  (void)scratch; (void)scratch_bytes;
+  es_b200::RowScatter dense = {};
+  return es_b200::grouped_mm_impl(a, b, sfa, sfb, d, out_dtype, problem_sizes, expert_offsets, blockscale_offsets,
+                                  num_experts, num_rows, n, k, sfa_rows, dense, stream);
+}
+
+extern "C" int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
+                                                int out_dtype, const int32_t* problem_sizes,
+                                                const int32_t* expert_offsets, const int32_t* blockscale_offsets,
+                                                int num_experts, int64_t num_rows, int n, int k, int64_t sfa_rows,
+                                                const int32_t* row_meta, const void* const* peer_out, int world,
+                                                int64_t slots_per_gpu, void* stream) {
+  using namespace es_b200;
+  ES_REQUIRE(world >= 1 && world <= SCATTER_MAX_GPUS, "world size must be in [1, %d]", SCATTER_MAX_GPUS);
+  ES_REQUIRE(row_meta && peer_out, "null pointer argument");
+  ES_REQUIRE((reinterpret_cast<uintptr_t>(row_meta) & 7u) == 0, "row_meta must be 8-byte aligned");
+  ES_REQUIRE(slots_per_gpu >= 0, "slots_per_gpu out of range");
+  RowScatter sc = {};
+  sc.meta = reinterpret_cast<const int2*>(row_meta);
+  sc.gpus = world;
+  sc.slots = slots_per_gpu;
+  for (int i = 0; i < world; ++i) {
+    ES_REQUIRE(peer_out[i] != nullptr && aligned16(peer_out[i]), "peer output %d must be a 16-byte aligned pointer", i);
+    sc.base[i] = const_cast<void*>(peer_out[i]);
+  }
+  return grouped_mm_impl(a, b, sfa, sfb, nullptr, out_dtype, problem_sizes, expert_offsets, blockscale_offsets,
+                         num_experts, num_rows, n, k, sfa_rows, sc, stream);
 }
 
 extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {

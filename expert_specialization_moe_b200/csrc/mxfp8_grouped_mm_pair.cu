@@ -151,7 +151,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict__ d,
                              const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
                              const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
-                             int wait_at_start) {
+                             int wait_at_start, const __grid_constant__ RowScatter scatter) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 8 x 1 KB, one per epilogue warp
@@ -403,7 +403,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
                                          ptx::tc_fence_before_sync();
                                          __syncwarp();
                                          if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[sub], 0);   // leader's barrier
-                                       });
+                                       }, scatter, ti.row0 + sub * SUB_TILE, nt * TILE_N + q * 32, &g_status);
     }
   }
 
@@ -414,13 +414,14 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     __syncwarp();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+  if (scatter.meta != nullptr) __threadfence_system();   // rows may have gone to other GPUs
   if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
 }
 
 template <typename OutT>
 int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
            const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int64_t sfa_rows,
-           int min_rows, int wait_at_start, cudaStream_t stream) {
+           int min_rows, int wait_at_start, const RowScatter& scatter, cudaStream_t stream) {
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
@@ -478,21 +479,22 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   const int clusters = (int)(max_tiles < max_clusters ? max_tiles : max_clusters);
   cfg.gridDim = dim3(2 * clusters);
   cfg.numAttrs = 2;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows, wait_at_start));
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows,
+                                 wait_at_start, scatter));
   return ES_B200_OK;
 }
 
 int launch_bf16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
                 const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, int min_rows, int wait_at_start, cudaStream_t stream) {
+                int64_t sfa_rows, int min_rows, int wait_at_start, const RowScatter& scatter, cudaStream_t stream) {
   return launch<__nv_bfloat16>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows,
-                               wait_at_start, stream);
+                               wait_at_start, scatter, stream);
 }
 int launch_fp16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
                 const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, int min_rows, int wait_at_start, cudaStream_t stream) {
+                int64_t sfa_rows, int min_rows, int wait_at_start, const RowScatter& scatter, cudaStream_t stream) {
   return launch<__half>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows, wait_at_start,
-                        stream);
+                        scatter, stream);
 }
 
 #ifdef ES_PROFILE

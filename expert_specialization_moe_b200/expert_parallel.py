@@ -190,10 +190,12 @@ class ExpertShard:
         return codes.view(e, n, k), sf
 
     def forward_codes(self, a: torch.Tensor, sfa: torch.Tensor, rows: torch.Tensor, eo: torch.Tensor,
-                      bo: torch.Tensor, work: dict) -> torch.Tensor:
+                      bo: torch.Tensor, work: dict, scatter=None) -> Optional[torch.Tensor]:
         """a [capacity, H] e4m3 + sfa (swizzled) as delivered by FusedExchange.dispatch, grouped by local expert with
         `rows[e]` valid rows at expert_offsets eo / blockscale_offsets bo (all on the device).  `work` caches the
-        capacity-sized intermediates.  Returns [capacity, H] (rows past the valid ones are undefined)."""
+        capacity-sized intermediates.  Returns [capacity, H] (rows past the valid ones are undefined) — or, with
+        `scatter` = (row_meta, peer table, world, slots), nothing: the down GEMM then stores every output row
+        straight into its (GPU, slot) destination (es_b200_mxfp8_grouped_mm_scatter)."""
         from .ops import es_sm100_mxfp8_blockscaled_grouped_mm as mm
         from .ops import es_sm100_mxfp8_silu_mul_grouped_quant as silu_mul_quant
         cap, dev = a.shape[0], a.device
@@ -202,14 +204,24 @@ class ExpertShard:
             work.update(cap=cap,
                         h1=torch.empty((cap, self.n1), dtype=torch.bfloat16, device=dev),
                         a2=torch.empty((cap, self.i), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
-                        sfa2=torch.zeros((sfa.shape[0], self.i // 32), dtype=torch.uint8, device=dev),
-                        out=torch.empty((cap, self.h), dtype=torch.bfloat16, device=dev))
+                        sfa2=torch.zeros((sfa.shape[0], self.i // 32), dtype=torch.uint8, device=dev))
         ps1 = torch.stack([rows, torch.full_like(rows, self.n1), torch.full_like(rows, self.h)], dim=1).contiguous()
         ps2 = torch.stack([rows, torch.full_like(rows, self.h), torch.full_like(rows, self.i)], dim=1).contiguous()
         mm(work["h1"], a, self.w1.transpose(1, 2), sfa, self.sf1, ps1, eo, bo)
         silu_mul_quant(work["h1"], ps2, eo, bo, work["a2"], work["sfa2"])
-        mm(work["out"], work["a2"], self.w2.transpose(1, 2), work["sfa2"], self.sf2, ps2, eo, bo)
-        return work["out"]
+        if scatter is None:
+            if "out" not in work:
+                work["out"] = torch.empty((cap, self.h), dtype=torch.bfloat16, device=dev)
+            mm(work["out"], work["a2"], self.w2.transpose(1, 2), work["sfa2"], self.sf2, ps2, eo, bo)
+            return work["out"]
+        from . import _cabi
+        meta, table, world, slots = scatter
+        _cabi.check(_cabi.load().es_b200_mxfp8_grouped_mm_scatter(
+            work["a2"].data_ptr(), self.w2.data_ptr(), work["sfa2"].data_ptr(), self.sf2.data_ptr(), _cabi.BF16,
+            ps2.data_ptr(), eo.data_ptr(), bo.data_ptr(), self.e_local, cap, self.h, self.i,
+            work["sfa2"].numel() // (self.i // 32), meta.data_ptr(), table, world, slots,
+            torch.cuda.current_stream(dev).cuda_stream))
+        return None
 
     def forward(self, x: torch.Tensor, plan: DispatchPlan) -> torch.Tensor:
         """x [rows_in, H] bf16 grouped by local expert -> [rows_in, H] bf16."""
@@ -338,16 +350,29 @@ class FusedExchange:
         self._check(self._lib.es_b200_ep_combine_push(
             y.data_ptr(), self.meta.data_ptr(), plan["total_rows"].data_ptr(), self._peer_pairs, self.world,
             self.capacity, self.tokens * self.topk, self.hidden, 2, s))
-        self.barrier(y.device)
-        out = torch.empty((self.tokens, self.hidden), dtype=self.dtype, device=y.device)
+        return self.reduce(topk_weights)
+
+    def reduce(self, topk_weights: torch.Tensor) -> torch.Tensor:
+        """After every rank's expert outputs have arrived in my (token, j) slots: out[t] = sum_j w[t, j] * slot(t, j)."""
+        dev = self.pairs.device
+        self.barrier(dev)
+        out = torch.empty((self.tokens, self.hidden), dtype=self.dtype, device=dev)
         w = topk_weights.to(torch.float32).contiguous()
         self._check(self._lib.es_b200_ep_topk_weighted_sum(self.pairs.data_ptr(), self._dtype_code, w.data_ptr(),
-                                                           out.data_ptr(), self.tokens, self.topk, self.hidden, s))
+                                                           out.data_ptr(), self.tokens, self.topk, self.hidden,
+                                                           torch.cuda.current_stream(dev).cuda_stream))
         return out
 
-    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
-                shard: ExpertShard) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, shard: ExpertShard,
+                fuse_combine: bool = True) -> torch.Tensor:
+        """One MoE layer.  With fuse_combine the down GEMM's epilogue stores each output row straight into the
+        sender's slot; otherwise the rows go through a dense output and es_b200_ep_combine_push."""
+        assert self.dtype == torch.bfloat16 or not fuse_combine
         plan = self.plan(topk_ids)
         a, sfa = self.dispatch(x, plan)
-        y = shard.forward_codes(a, sfa, plan["rows"], plan["expert_offsets"], plan["blockscale_offsets"], self.work)
+        scatter = (self.meta, self._peer_pairs, self.world, self.tokens * self.topk) if fuse_combine else None
+        y = shard.forward_codes(a, sfa, plan["rows"], plan["expert_offsets"], plan["blockscale_offsets"], self.work,
+                                scatter)
+        if fuse_combine:
+            return self.reduce(topk_weights)
         return self.combine(y, plan, topk_weights)

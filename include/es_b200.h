@@ -121,6 +121,19 @@ int es_b200_fp8_blockwise_grouped_mm(const void* a, const void* b, const float* 
                                      void* scratch, size_t scratch_bytes, void* stream);
 
 /*
+ * es_b200_mxfp8_grouped_mm with the expert-parallel combine fused into its epilogue: same operands and problem
+ * description, but output row r is stored to row row_meta[2r+1] of the [slots_per_gpu, n] array
+ * peer_out[row_meta[2r]] (HOST array of `world` device pointers: the GPUs' pair buffers mapped into this process)
+ * instead of row r of a dense d — the (GPU, slot) pairs es_b200_ep_dispatch_quant_push delivered with the rows.
+ * Entries out of range are skipped and reported by es_b200_check_status.  No counterpart in the reference.
+ */
+int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
+                                     int out_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
+                                     const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n,
+                                     int k, int64_t sfa_rows, const int32_t* row_meta, const void* const* peer_out,
+                                     int world, int64_t slots_per_gpu, void* stream);
+
+/*
  * Expert-parallel exchange over peer memory (one process per GPU; the experts of a layer are spread over the GPUs of a
  * node).  No counterpart in the reference, which has no distributed code: these three calls replace what a caller
  * would otherwise build from an all-to-all, a permutation and es_sm100_mxfp8_blockscaled_grouped_quant

@@ -116,10 +116,14 @@ def _worker_fused(rank, world, port, q):
                 idx = (base.unsqueeze(1) + torch.arange(kt, device=dev).unsqueeze(0) * 512).unsqueeze(2) \
                     + torch.arange(4, device=dev).view(1, 1, 4)
                 assert torch.equal(sfa.reshape(-1)[idx], sf_ref.reshape(-1)[idx]), f"scales of local expert {le} differ"
-            out = fx.forward(x, ids, wts, shard)
-            torch.cuda.synchronize()
-            worst = max(worst, float((out.float() - out_ref.float()).abs().max()
-                                     / out_ref.float().abs().max().clamp_min(1e-6)))
+            for fuse in (False, True):            # combine as its own kernel / fused into the down GEMM's epilogue
+                out = fx.forward(x, ids, wts, shard, fuse_combine=fuse)
+                torch.cuda.synchronize()
+                worst = max(worst, float((out.float() - out_ref.float()).abs().max()
+                                         / out_ref.float().abs().max().clamp_min(1e-6)))
+                if fuse:
+                    assert torch.equal(out, out_unfused), "fused and unfused combine differ"
+                out_unfused = out
         raw = ctypes.c_uint32(0)
         rc = _cabi.load().es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
         q.put((rank, worst if rc == 0 else float("inf"), None))
