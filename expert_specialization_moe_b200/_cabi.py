@@ -57,6 +57,9 @@ def _declare(lib):
     lib.es_b200_ep_route_count.restype = c_int
     lib.es_b200_ep_route_count.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, POINTER(c_void_p), c_int,
                                            c_int, c_void_p]
+    lib.es_b200_ep_route_count_static.restype = c_int
+    lib.es_b200_ep_route_count_static.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, POINTER(c_void_p), c_int,
+                                                  c_int, c_void_p]
     lib.es_b200_ep_route_tables.restype = c_int
     lib.es_b200_ep_route_tables.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -210,3 +210,39 @@ extern "C" int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, 
   ES_CUDA_TRY(cudaGetLastError());
   return ES_B200_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// es_b200_ep_route_count for callers that cannot hand over scratch memory.
+//
+// The histogram step needs 256 x num_experts counters that are neither an input nor a result.  A serving process
+// whose memory manager has claimed the whole GPU up front, or a host binding (cgo, JNI, a plugin ABI) that is given
+// raw pointers by its caller and has no device allocator of its own, has nowhere to take them from on the request
+// path.  For those callers the counters live in the library image: one array per GPU that loads the library, held
+// until the process exits, sized for at most ES_B200_ROUTE_STATIC_MAX_EXPERTS experts (256 KB).
+//
+// `g_route_static_counts` is a device symbol: in host code its name is only a handle.  Its device address is looked
+// up once per device (cudaGetSymbolAddress, with that device current) by the first call on that device and cached.
+// All calls on a device share the array: two calls that overlap on the GPU (different streams) would overwrite each
+// other's counters.  Nothing has to be cleared between calls — the count kernel writes every counter it later reads.
+static __device__ __align__(256) int32_t g_route_static_counts[es_b200::route::SEGMENTS * ES_B200_ROUTE_STATIC_MAX_EXPERTS];
+
+extern "C" int es_b200_ep_route_count_static(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
+                                             int32_t* segment_base, const void* const* peer_counts_all, int my_rank,
+                                             int world, void* stream) {
+  using namespace es_b200;
+  ES_REQUIRE(num_experts >= 1 && num_experts <= ES_B200_ROUTE_STATIC_MAX_EXPERTS,
+             "es_b200_ep_route_count_static holds counters for at most %d experts (got %d); use "
+             "es_b200_ep_route_count with caller-provided scratch for more",
+             ES_B200_ROUTE_STATIC_MAX_EXPERTS, num_experts);
+  static int32_t* counters_of_device[64] = {nullptr};
+  int dev = 0;
+  ES_CUDA_TRY(cudaGetDevice(&dev));
+  ES_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+  if (counters_of_device[dev] == nullptr) {
+    int32_t* p = nullptr;
+    ES_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_static_counts));
+    counters_of_device[dev] = p;
+  }
+  return es_b200_ep_route_count(topk_ids, ids_are_int64, pairs, num_experts, counters_of_device[dev], segment_base,
+                                peer_counts_all, my_rank, world, stream);
+}

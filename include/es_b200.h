@@ -190,6 +190,22 @@ int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, int pairs, 
                             int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* total_rows, void* stream);
 
 /*
+ * es_b200_ep_route_count without caller-provided scratch (no counterpart in the reference).  For callers that cannot
+ * allocate device memory where they call this library — a server whose memory manager owns the whole GPU, a cgo / JNI /
+ * plugin binding that only ever receives raw pointers — the 256 x num_experts histogram counters live in a static
+ * device array inside the library (256 KB per GPU, held until the process exits) instead of `segment_counts`.
+ * Limits and rules: num_experts <= ES_B200_ROUTE_STATIC_MAX_EXPERTS, otherwise ES_B200_ERR_INVALID_ARGUMENT and
+ * nothing is launched; the call allocates and frees nothing; the first call on each device looks up the array's device
+ * address (make that first call outside any stream capture); all calls on one device share the array, so calls that
+ * overlap on the GPU (different streams) race — serialise them.  Inputs, outputs and results are those of
+ * es_b200_ep_route_count.
+ */
+#define ES_B200_ROUTE_STATIC_MAX_EXPERTS 256
+int es_b200_ep_route_count_static(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
+                                  int32_t* segment_base, const void* const* peer_counts_all, int my_rank, int world,
+                                  void* stream);
+
+/*
  * Device-side status word of the grouped GEMMs.  Every wait inside the kernels is bounded; a wait that gives up
  * sets a bit in a library-owned device word and the kernel exits cleanly.  This call synchronises `stream`, copies
  * that word to the host, clears it, and returns ES_B200_OK or ES_B200_ERR_DEVICE_TIMEOUT.  Optional: intended for
