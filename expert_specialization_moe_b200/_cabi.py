@@ -63,7 +63,7 @@ def _declare(lib):
     lib.es_b200_ep_route_tables.restype = c_int
     lib.es_b200_ep_route_tables.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                            c_void_p]
+                                            c_int64, c_void_p]
     lib.es_b200_check_status.restype = c_int
     lib.es_b200_check_status.argtypes = [c_void_p, POINTER(c_uint32)]
 

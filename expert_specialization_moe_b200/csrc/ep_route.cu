@@ -22,6 +22,9 @@ constexpr int THREADS = WARPS * 32;
 constexpr int BLOCKS = 32;
 constexpr int SEGMENTS = BLOCKS * WARPS;       // 256
 constexpr int MAX_WORLD = 16;
+constexpr uint32_t ERR_CAPACITY = 0x80000u;    // more rows were routed to this GPU than its receive buffers hold
+
+__device__ uint32_t g_status = 0;
 
 struct PeerTable {
   void* ptr[MAX_WORLD];
@@ -81,7 +84,8 @@ __global__ void __launch_bounds__(THREADS)
 tables_kernel(const void* __restrict__ ids, int ids_int64, int pairs, int num_experts, const int* __restrict__ seg_base,
               const int* __restrict__ counts_all, int my_rank, int world, int k, int* __restrict__ dst_rank,
               int* __restrict__ dst_row, long long* __restrict__ dst_scale_offset, int* __restrict__ rows_out,
-              int* __restrict__ eo_out, int* __restrict__ bo_out, int* __restrict__ total_rows_out) {
+              int* __restrict__ eo_out, int* __restrict__ bo_out, int* __restrict__ total_rows_out,
+              long long capacity_rows) {
   // shared: row_base[E] (row of the expert's first row from THIS GPU in the owner's buffer), sc_base[E] (scale-row
   // offset of the expert on its owner), in_expert[E] (rows of lower-ranked GPUs inside the expert), run[WARPS][E]
   extern __shared__ int sh[];
@@ -114,14 +118,20 @@ tables_kernel(const void* __restrict__ ids, int ids_int64, int pairs, int num_ex
       eo_s[e] = rows;
       bo_s[e] = srows;
       if (d == my_rank && blockIdx.x == 0) {
-        rows_out[le] = m;
+        // Rows past the capacity of the receive buffers are dropped (the senders' stores to them are skipped by the
+        // dispatch kernel's own range check): the expert that straddles the end is cut, later ones get no rows.
+        long long room = capacity_rows - rows;
+        if (room < 0) room = 0;
+        const int kept = m < room ? m : (int)room;
+        if (kept != m) atomicOr(&g_status, ERR_CAPACITY);
+        rows_out[le] = kept;
         eo_out[le] = rows;
         bo_out[le] = srows;
       }
       rows += m;
       srows += (m + 127) & ~127;
     }
-    if (d == my_rank && blockIdx.x == 0) *total_rows_out = rows;
+    if (d == my_rank && blockIdx.x == 0) *total_rows_out = rows < capacity_rows ? rows : (int)capacity_rows;
   }
   const int seg = blockIdx.x * WARPS + warp;
   int* my_run = run + warp * num_experts;
@@ -159,6 +169,17 @@ tables_kernel(const void* __restrict__ ids, int ids_int64, int pairs, int num_ex
   }
 }
 
+int read_and_clear_status(uint32_t* out) {
+  uint32_t v = 0;
+  ES_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_status, sizeof(v)));
+  if (v != 0) {
+    uint32_t zero = 0;
+    ES_CUDA_TRY(cudaMemcpyToSymbol(g_status, &zero, sizeof(zero)));
+  }
+  *out = v;
+  return ES_B200_OK;
+}
+
 }  // namespace route
 }  // namespace es_b200
 
@@ -192,7 +213,7 @@ extern "C" int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, 
                                        const int32_t* segment_base, const int32_t* counts_all, int my_rank, int world,
                                        int k, int32_t* dst_rank, int32_t* dst_row, int64_t* dst_scale_offset,
                                        int32_t* rows, int32_t* expert_offsets, int32_t* blockscale_offsets,
-                                       int32_t* total_rows, void* stream) {
+                                       int32_t* total_rows, int64_t capacity_rows, void* stream) {
   using namespace es_b200;
   ES_REQUIRE(world >= 1 && world <= route::MAX_WORLD, "world size must be in [1, %d]", route::MAX_WORLD);
   ES_REQUIRE(my_rank >= 0 && my_rank < world, "rank out of range");
@@ -200,13 +221,15 @@ extern "C" int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, 
              "num_experts must be a multiple of the world size and at most %d", ES_B200_MAX_EXPERTS);
   ES_REQUIRE(k > 0 && k % 128 == 0, "k must align to 128");
   ES_REQUIRE(pairs >= 0, "pairs out of range");
+  ES_REQUIRE(capacity_rows > 0 && capacity_rows < (int64_t)1 << 31, "capacity_rows out of range");
   ES_REQUIRE(topk_ids && segment_base && counts_all && dst_rank && dst_row && dst_scale_offset && rows &&
                  expert_offsets && blockscale_offsets && total_rows,
              "null pointer argument");
   const size_t smem = (size_t)(3 + route::WARPS) * num_experts * sizeof(int);
   route::tables_kernel<<<route::BLOCKS, route::THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
       topk_ids, ids_are_int64, pairs, num_experts, segment_base, counts_all, my_rank, world, k, dst_rank, dst_row,
-      reinterpret_cast<long long*>(dst_scale_offset), rows, expert_offsets, blockscale_offsets, total_rows);
+      reinterpret_cast<long long*>(dst_scale_offset), rows, expert_offsets, blockscale_offsets, total_rows,
+      capacity_rows);
   ES_CUDA_TRY(cudaGetLastError());
   return ES_B200_OK;
 }

@@ -338,6 +338,9 @@ int read_and_clear_status(uint32_t* out);
 namespace ep {    // expert-parallel dispatch / combine kernels (ep_dispatch_combine.cu)
 int read_and_clear_status(uint32_t* out);
 }
+namespace route {  // expert-parallel routing tables (ep_route.cu)
+int read_and_clear_status(uint32_t* out);
+}
 namespace bw {    // FP8-blockwise kernel (fp8_blockwise_grouped_mm.cu)
 int read_and_clear_status(uint32_t* out);
 }
@@ -463,6 +466,9 @@ extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {
   if (rc2 != ES_B200_OK) return rc2;
   v |= v2;
   rc2 = ep::read_and_clear_status(&v2);
+  if (rc2 != ES_B200_OK) return rc2;
+  v |= v2;
+  rc2 = route::read_and_clear_status(&v2);
   if (rc2 != ES_B200_OK) return rc2;
   v |= v2;
   if (raw_status) *raw_status = v;

@@ -329,7 +329,7 @@ class FusedExchange:
             topk_ids.data_ptr(), is64, pairs, self.num_experts, self._seg_base.data_ptr(), self.counts_all.data_ptr(),
             self.rank, self.world, self.hidden, t["dst_rank"].data_ptr(), t["dst_row"].data_ptr(),
             t["dst_scale_offset"].data_ptr(), t["rows"].data_ptr(), t["expert_offsets"].data_ptr(),
-            t["blockscale_offsets"].data_ptr(), t["total_rows"].data_ptr(), s))
+            t["blockscale_offsets"].data_ptr(), t["total_rows"].data_ptr(), self.capacity, s))
         return t
 
     def dispatch(self, x: torch.Tensor, plan: dict):

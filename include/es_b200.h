@@ -179,7 +179,9 @@ int es_b200_ep_barrier(const void* const* peer_flags, int my_rank, int world, vo
  *   es_b200_ep_dispatch_quant_push; an id outside [0, E) gives owner -1, which that call reports and skips), and for
  *   this GPU's own experts: rows[e], expert_offsets[e], blockscale_offsets[e] (E/world entries each) and total_rows[0]
  *   — the problem description of the grouped GEMMs that follow.  On the owner, rows are ordered by expert, then
- *   source GPU, then pair index.
+ *   source GPU, then pair index.  capacity_rows = rows this GPU's receive buffers hold: if more are routed to it, the
+ *   surplus is dropped (rows[] is cut so that no operator downstream touches a row past the capacity) and
+ *   es_b200_check_status reports it.
  */
 int es_b200_ep_route_count(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
                            int32_t* segment_counts, int32_t* segment_base, const void* const* peer_counts_all,
@@ -187,7 +189,8 @@ int es_b200_ep_route_count(const void* topk_ids, int ids_are_int64, int pairs, i
 int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
                             const int32_t* segment_base, const int32_t* counts_all, int my_rank, int world, int k,
                             int32_t* dst_rank, int32_t* dst_row, int64_t* dst_scale_offset, int32_t* rows,
-                            int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* total_rows, void* stream);
+                            int32_t* expert_offsets, int32_t* blockscale_offsets, int32_t* total_rows,
+                            int64_t capacity_rows, void* stream);
 
 /*
  * es_b200_ep_route_count without caller-provided scratch (no counterpart in the reference).  For callers that cannot

@@ -169,3 +169,38 @@ def test_two_gpu_moe_layer():
     for rank, diff, tb in res:
         assert tb is None, f"rank {rank}:\n{tb}"
         assert diff < 5e-3, f"rank {rank}: calc_diff {diff}"
+
+
+def test_route_tables_cut_rows_at_the_capacity():
+    """More rows routed to a GPU than its receive buffers hold (one GPU, through the C ABI): the problem description
+    handed to the GEMMs stops at the capacity, the surplus pairs keep destinations past it (which the dispatch kernel
+    skips), and es_b200_check_status reports the overflow once."""
+    import ctypes
+    from expert_specialization_moe_b200 import _cabi
+    lib = _cabi.load()
+    dev = torch.device("cuda", 0)
+    E, tokens, topk, H, capacity = 8, 64, 2, 256, 100
+    g = torch.Generator(device=dev).manual_seed(3)
+    ids = torch.randint(0, E, (tokens, topk), generator=g, device=dev, dtype=torch.int64)
+    pairs = tokens * topk
+    i32 = lambda *s: torch.zeros(s, dtype=torch.int32, device=dev)
+    seg_counts, seg_base, counts_all = i32(256, E), i32(256, E), i32(1, E)
+    dst_rank, dst_row, rows, eo, bo, total = i32(pairs), i32(pairs), i32(E), i32(E), i32(E), i32(1)
+    sf_off = torch.zeros(pairs, dtype=torch.int64, device=dev)
+    table = (ctypes.c_void_p * 1)(counts_all.data_ptr())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    raw = ctypes.c_uint32(0)
+    lib.es_b200_check_status(stream, ctypes.byref(raw))          # start from a clean status word
+    assert lib.es_b200_ep_route_count(ids.data_ptr(), 1, pairs, E, seg_counts.data_ptr(), seg_base.data_ptr(), table,
+                                      0, 1, stream) == 0
+    assert lib.es_b200_ep_route_tables(ids.data_ptr(), 1, pairs, E, seg_base.data_ptr(), counts_all.data_ptr(), 0, 1, H,
+                                       dst_rank.data_ptr(), dst_row.data_ptr(), sf_off.data_ptr(), rows.data_ptr(),
+                                       eo.data_ptr(), bo.data_ptr(), total.data_ptr(), capacity, stream) == 0
+    assert lib.es_b200_check_status(stream, ctypes.byref(raw)) != 0 and raw.value != 0
+    assert lib.es_b200_check_status(stream, ctypes.byref(raw)) == 0
+    assert int(total) == capacity and int(rows.sum()) == capacity
+    counts = torch.bincount(ids.reshape(-1), minlength=E)
+    assert torch.equal(eo.to(torch.int64), torch.cumsum(counts, 0) - counts)       # offsets are those of the full problem
+    assert bool(((rows == 0) | ((eo + rows) <= capacity)).all())
+    assert int((dst_row >= capacity).sum()) == pairs - capacity
+    assert sorted(dst_row.tolist()) == list(range(pairs))
