@@ -273,10 +273,11 @@ def bench_ep_layer(args, device, rank, world, dist):
     """Qwen3-30B-A3B-shaped MoE layer, expert parallel: E=128, top-8, hidden 2048, moe_intermediate 768, 16384 tokens
     per GPU, router logits N(0,1) -> softmax -> top-8.  One step = count exchange + NCCL all-to-all dispatch + grouped
     quant + gate_up grouped GEMM + fused SiLU*mul/requant + down grouped GEMM + all-to-all combine with top-k weights
-    (expert_parallel.moe_forward).  Needs N >= 2 ranks; value = expert-GEMM FLOPs of all ranks / step time."""
+    (expert_parallel.moe_forward), or the same layer over peer memory (expert_parallel.FusedExchange).  value =
+    expert-GEMM FLOPs of all ranks / step time."""
     from expert_specialization_moe_b200 import expert_parallel as ep
     E, topk, H, I, tokens = 128, 8, 2048, 768, 16384
-    assert dist is not None and E % world == 0, "the expert-parallel layer benchmark needs 2, 4 or 8 ranks"
+    assert dist is not None and E % world == 0, "the expert-parallel layer benchmark runs on 1, 2, 4 or 8 ranks"
     e_local = E // world
     g = torch.Generator(device=device); g.manual_seed(1234)           # same weights everywhere; each rank keeps a shard
     w1 = (torch.randn((E, 2 * I, H), generator=g, device=device) * 0.02).to(torch.bfloat16)
@@ -584,6 +585,14 @@ def main():
     if args.workload.startswith("quant"):
         return bench_quant(args, E, T, K, desc, device, rank, world, dist)
     if args.workload.startswith("qwen3_ep"):
+        if dist is None:                         # one GPU: a process group of one, all experts local
+            import socket
+            import torch.distributed as dist
+            with socket.socket() as sock:
+                sock.bind(("127.0.0.1", 0))
+                port = sock.getsockname()[1]
+            dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                                    device_id=device)
         return bench_ep_layer(args, device, rank, world, dist)
     if args.workload.startswith("blockwise"):
         return bench_blockwise(args, E, T, N, K, desc, device, rank, world, dist)

@@ -54,6 +54,10 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
     for (int h = 0; h < 2; ++h) {
       const int c = c0 + h * 32;
       if (c >= n_cols) break;
+      // scatter map: lane l fetches the destination of token c + l now, so that the load's latency hides behind the
+      // TMEM read and the conversions; the store loop below picks it up with a shuffle
+      int2 dest = make_int2(-1, -1);
+      if (scatter.meta != nullptr && do_store && c + lane < valid) dest = scatter.meta[first_row + c + lane];
       ptx::tc_wait_ld();                                    // chunk c is in registers (va if h == 0, vb otherwise)
       const bool more = c + 32 < n_cols;
       if (more) {
@@ -73,13 +77,14 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
             const int tok = it * 8 + (lane >> 2);
             const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
             const int row = c + p * TOK + tok;
-            if (row < valid) {
-              if (scatter.meta == nullptr) {
-                *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
-              } else {
-                const int2 m = scatter.meta[first_row + row];
-                if (m.x >= 0 && m.x < scatter.gpus && m.y >= 0 && m.y < scatter.slots)
-                  *reinterpret_cast<uint4*>(static_cast<OutT*>(scatter.base[m.x]) + (int64_t)m.y * ld + col_off + part * 8) = val;
+            if (scatter.meta == nullptr) {
+              if (row < valid) *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
+            } else {
+              const int gpu = __shfl_sync(0xffffffffu, dest.x, p * TOK + tok);
+              const int slot = __shfl_sync(0xffffffffu, dest.y, p * TOK + tok);
+              if (row < valid) {
+                if (gpu >= 0 && gpu < scatter.gpus && slot >= 0 && slot < scatter.slots)
+                  *reinterpret_cast<uint4*>(static_cast<OutT*>(scatter.base[gpu]) + (int64_t)slot * ld + col_off + part * 8) = val;
                 else
                   atomicOr(status, ERR_SCATTER_DESTINATION);
               }
