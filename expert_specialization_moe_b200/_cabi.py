@@ -45,8 +45,12 @@ def _declare(lib):
                                                      c_size_t, c_void_p]
     lib.es_b200_ep_dispatch_quant_push.restype = c_int
     lib.es_b200_ep_dispatch_quant_push.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, POINTER(c_void_p),
-                                                   POINTER(c_void_p), POINTER(c_void_p), c_int, c_int, c_int, c_int,
-                                                   c_int, c_int64, c_int64, c_void_p]
+                                                   POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int, c_int64,
+                                                   c_void_p]
+    lib.es_b200_ep_side_record_bytes.restype = c_int
+    lib.es_b200_ep_side_record_bytes.argtypes = [c_int]
+    lib.es_b200_ep_unpack_side.restype = c_int
+    lib.es_b200_ep_unpack_side.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_void_p]
     lib.es_b200_ep_combine_push.restype = c_int
     lib.es_b200_ep_combine_push.argtypes = [c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int, c_int64, c_int64,
                                             c_int, c_int, c_void_p]

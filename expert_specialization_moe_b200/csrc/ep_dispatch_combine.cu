@@ -3,9 +3,13 @@
 // + quantisation sequence when the experts of one MoE layer are spread over the GPUs of a node.
 //
 //   dispatch  es_b200_ep_dispatch_quant_push: every token row is quantised ONCE (MXFP8, same arithmetic as the grouped
-//             quant kernel) and its codes, its scale words (already at their swizzled position) and its return
-//             address are stored straight into the receive buffers of the GPUs that own its top-k experts —
-//             1.03 bytes per element cross NVLink instead of 2, and no bf16 copy of the routed rows ever exists.
+//             quant kernel) and its codes plus one small side record (return address, position of its scales in the
+//             owner's swizzled scale buffer, its k/32 scale bytes) are stored straight into the receive buffers of
+//             the GPUs that own its top-k experts — 1.03 bytes per element cross NVLink instead of 2, and no bf16
+//             copy of the routed rows ever exists.  The side record travels as one contiguous piece: sixteen
+//             separate 4-byte scale stores per row cost a third of the dispatch time over NVLink (measured).
+//   unpack    es_b200_ep_unpack_side (local, after the barrier): scale bytes of the received rows -> swizzled scale
+//             buffer, return addresses -> the (GPU, slot) table the combine reads.
 //   combine   es_b200_ep_combine_push: every expert-output row is stored into the (token, j) slot of the GPU the token
 //             came from.
 //   reduce    es_b200_ep_topk_weighted_sum: out[t] = sum_j w[t, j] * pairs[t, j], fp32 accumulation.
@@ -42,20 +46,28 @@ __device__ __forceinline__ void st_8B(void* p, uint2 v) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
-// One warp per token row.  Per pass a lane holds 4 x 8 elements (1024 elements per warp); the codes and scale words of
-// the pass stay in registers while they are stored to each of the row's top-k destinations.
+// Side record of a received row: { int32 source GPU, int32 pair index, int64 byte offset of the row's scale word for
+// K tile 0 in the owner's swizzled scale buffer, k/32 scale bytes }, padded to a multiple of 16 bytes.
+__host__ __device__ __forceinline__ int side_record_bytes(int k) { return 16 + (((k >> 5) + 15) & ~15); }
+constexpr int MAX_SIDE_BYTES = 16 + 512;        // k <= 16384
+
+// One warp per token row.  Per pass a lane holds 4 x 8 elements (1024 elements per warp); the codes of the pass stay
+// in registers while they are stored to each of the row's top-k destinations, the scale words collect in a per-warp
+// shared-memory copy of the side record, which goes out once per destination after the last pass.
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
                            const long long* __restrict__ dst_sf_offset, const __grid_constant__ PeerTable codes,
-                           const __grid_constant__ PeerTable scales,
-                           const __grid_constant__ PeerTable meta, int my_rank, int world, int tokens, int topk, int k,
-                           long long capacity_rows, long long scale_bytes) {
+                           const __grid_constant__ PeerTable side, int my_rank, int world, int tokens, int topk, int k,
+                           long long capacity_rows) {
+  __shared__ __align__(16) uint8_t side_s[THREADS / 32][MAX_SIDE_BYTES];
   pdl_wait_prior_grid();
   pdl_launch_dependents();
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int warps_per_grid = gridDim.x * (THREADS / 32);
-  for (int t = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); t < tokens; t += warps_per_grid) {
+  const int side_bytes = side_record_bytes(k);
+  uint8_t* rec = side_s[warp];
+  for (int t = blockIdx.x * (THREADS / 32) + warp; t < tokens; t += warps_per_grid) {
     // lane j < topk holds destination j; bad destinations are dropped here, once
     int my_rank_j = -1, my_row_j = 0;
     long long my_sf_j = 0;
@@ -64,14 +76,9 @@ dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_
       my_rank_j = dst_rank[pair];
       my_row_j = dst_row[pair];
       my_sf_j = dst_sf_offset[pair];
-      const bool ok = my_rank_j >= 0 && my_rank_j < world && my_row_j >= 0 && my_row_j < capacity_rows &&
-                      my_sf_j >= 0 && my_sf_j + (long long)((k >> 7) - 1) * 512 + 4 <= scale_bytes && (my_sf_j & 3) == 0;
-      if (!ok) {
+      if (!(my_rank_j >= 0 && my_rank_j < world && my_row_j >= 0 && my_row_j < capacity_rows)) {
         atomicOr(&g_status, ERR_BAD_DESTINATION);
         my_rank_j = -1;
-      } else {
-        int2* m = reinterpret_cast<int2*>(meta.ptr[my_rank_j]) + my_row_j;     // return address of the row
-        *m = make_int2(my_rank, pair);
       }
     }
     const T* in_row = x + (int64_t)t * k;
@@ -83,7 +90,6 @@ dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_
         raw[j] = col < k ? ld_stream_16B(in_row + col) : make_uint4(0, 0, 0, 0);
       }
       uint2 code[4];
-      uint32_t word[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint32_t sf = quantize8<T>(raw[j], code[j]);
@@ -91,27 +97,70 @@ dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_
         uint32_t w = sf << (((lane >> 2) & 3) * 8);
         w |= __shfl_xor_sync(0xffffffffu, w, 4);
         w |= __shfl_xor_sync(0xffffffffu, w, 8);
-        word[j] = w;
+        const int col = c0 + j * 256 + lane * 8;
+        if ((lane & 15) == 0 && col < k) *reinterpret_cast<uint32_t*>(rec + 16 + (col >> 7) * 4) = w;
       }
       for (int d = 0; d < topk; ++d) {
         const int rank = __shfl_sync(0xffffffffu, my_rank_j, d);
         const int row = __shfl_sync(0xffffffffu, my_row_j, d);
-        const long long sf_off = __shfl_sync(0xffffffffu, my_sf_j, d);
         if (rank < 0) continue;                                   // warp-uniform
         uint8_t* out_row = reinterpret_cast<uint8_t*>(codes.ptr[rank]) + (int64_t)row * k;
-        uint8_t* sf_row = reinterpret_cast<uint8_t*>(scales.ptr[rank]) + sf_off;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int col = c0 + j * 256 + lane * 8;
-          if (col < k) {
-            st_8B(out_row + col, code[j]);
-            if ((lane & 15) == 0) *reinterpret_cast<uint32_t*>(sf_row + (int64_t)(col >> 7) * 512) = word[j];
-          }
+          if (col < k) st_8B(out_row + col, code[j]);
         }
       }
     }
+    __syncwarp();
+    for (int d = 0; d < topk; ++d) {
+      const int rank = __shfl_sync(0xffffffffu, my_rank_j, d);
+      const int row = __shfl_sync(0xffffffffu, my_row_j, d);
+      const long long sf_off = __shfl_sync(0xffffffffu, my_sf_j, d);
+      if (rank < 0) continue;                                     // warp-uniform
+      uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(side.ptr[rank]) + (int64_t)row * side_bytes);
+      for (int i = lane; i < side_bytes / 16; i += 32) {
+        uint4 v;
+        if (i == 0) {
+          v = make_uint4((uint32_t)my_rank, (uint32_t)(t * topk + d), (uint32_t)(sf_off & 0xffffffffll),
+                         (uint32_t)(sf_off >> 32));
+        } else {
+          v = *reinterpret_cast<const uint4*>(rec + i * 16);
+        }
+        out[i] = v;
+      }
+    }
+    __syncwarp();                // the record is rewritten by the next row
   }
   __threadfence_system();      // the stores above are to other GPUs' memory
+}
+
+// One warp per received row: the side record's scale bytes go to their swizzled position, its return address to the
+// (GPU, slot) table.  Offsets are range-checked: a bad one is skipped and reported.
+__global__ void __launch_bounds__(THREADS)
+unpack_side_kernel(const uint8_t* __restrict__ side, const int* __restrict__ num_rows_dev, uint8_t* __restrict__ scales,
+                   int2* __restrict__ meta, int k, long long capacity_rows, long long scale_bytes) {
+  pdl_wait_prior_grid();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = gridDim.x * (THREADS / 32);
+  const int side_bytes = side_record_bytes(k);
+  const int kt = k >> 7;
+  long long rows = *num_rows_dev;
+  if (rows > capacity_rows) rows = capacity_rows;
+  for (long long r = blockIdx.x * (THREADS / 32) + (threadIdx.x >> 5); r < rows; r += warps_per_grid) {
+    const uint8_t* rec = side + r * side_bytes;
+    const uint4 head = *reinterpret_cast<const uint4*>(rec);
+    const long long sf_off = (long long)head.z | ((long long)head.w << 32);
+    if (lane == 0) meta[r] = make_int2((int)head.x, (int)head.y);
+    const bool ok = sf_off >= 0 && (sf_off & 3) == 0 && sf_off + (long long)(kt - 1) * 512 + 4 <= scale_bytes;
+    if (!ok) {
+      if (lane == 0) atomicOr(&g_status, ERR_BAD_DESTINATION);
+      continue;
+    }
+    for (int q = lane; q < kt; q += 32)
+      *reinterpret_cast<uint32_t*>(scales + sf_off + (long long)q * 512) = *reinterpret_cast<const uint32_t*>(rec + 16 + q * 4);
+  }
 }
 
 // One warp per expert-output row: 16-byte loads of the local row, 16-byte stores into the owner's pair buffer.
@@ -262,27 +311,27 @@ int read_and_clear_status(uint32_t* out) {
 }  // namespace ep
 }  // namespace es_b200
 
+extern "C" int es_b200_ep_side_record_bytes(int k) { return es_b200::ep::side_record_bytes(k); }
+
 extern "C" int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const int32_t* dst_rank,
                                               const int32_t* dst_row, const int64_t* dst_scale_offset,
-                                              const void* const* peer_codes, const void* const* peer_scales,
-                                              const void* const* peer_meta, int my_rank, int world, int tokens,
-                                              int topk, int k, int64_t capacity_rows, int64_t scale_bytes,
+                                              const void* const* peer_codes, const void* const* peer_side, int my_rank,
+                                              int world, int tokens, int topk, int k, int64_t capacity_rows,
                                               void* stream) {
   using namespace es_b200;
   ES_REQUIRE(x_dtype == ES_B200_BF16 || x_dtype == ES_B200_FP16, "dtype must be kFloat16 or kBFloat16");
-  ES_REQUIRE(k > 0 && k % 128 == 0, "k must align to 128");
+  ES_REQUIRE(k > 0 && k % 128 == 0 && k <= 16384, "k must align to 128 and be at most 16384");
   ES_REQUIRE(world >= 1 && world <= ep::MAX_WORLD, "world size must be in [1, %d]", ep::MAX_WORLD);
   ES_REQUIRE(my_rank >= 0 && my_rank < world, "rank out of range");
   ES_REQUIRE(topk >= 1 && topk <= ep::MAX_TOPK, "topk must be in [1, %d]", ep::MAX_TOPK);
   ES_REQUIRE(tokens >= 0 && (int64_t)tokens * topk < (int64_t)1 << 31, "tokens * topk out of range");
-  ES_REQUIRE(capacity_rows > 0 && capacity_rows < (int64_t)1 << 31 && scale_bytes > 0, "receive buffer sizes out of range");
+  ES_REQUIRE(capacity_rows > 0 && capacity_rows < (int64_t)1 << 31, "capacity_rows out of range");
   if (tokens == 0) return ES_B200_OK;
-  ES_REQUIRE(x && dst_rank && dst_row && dst_scale_offset && peer_codes && peer_scales && peer_meta, "null pointer argument");
+  ES_REQUIRE(x && dst_rank && dst_row && dst_scale_offset && peer_codes && peer_side, "null pointer argument");
   ES_REQUIRE(aligned16(x), "x must be 16-byte aligned");
-  ep::PeerTable codes, scales, meta;
+  ep::PeerTable codes, side;
   int rc = ep::fill_table(&codes, peer_codes, world);
-  if (rc == ES_B200_OK) rc = ep::fill_table(&scales, peer_scales, world);
-  if (rc == ES_B200_OK) rc = ep::fill_table(&meta, peer_meta, world);
+  if (rc == ES_B200_OK) rc = ep::fill_table(&side, peer_side, world);
   if (rc != ES_B200_OK) return rc;
   int grid = 1;
   rc = ep::grid_for(tokens, &grid);
@@ -291,11 +340,30 @@ extern "C" int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const 
   if (x_dtype == ES_B200_BF16)
     ep::dispatch_quant_push_kernel<__nv_bfloat16><<<grid, ep::THREADS, 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), dst_rank, dst_row, reinterpret_cast<const long long*>(dst_scale_offset),
-        codes, scales, meta, my_rank, world, tokens, topk, k, capacity_rows, scale_bytes);
+        codes, side, my_rank, world, tokens, topk, k, capacity_rows);
   else
     ep::dispatch_quant_push_kernel<__half><<<grid, ep::THREADS, 0, s>>>(
         static_cast<const __half*>(x), dst_rank, dst_row, reinterpret_cast<const long long*>(dst_scale_offset), codes,
-        scales, meta, my_rank, world, tokens, topk, k, capacity_rows, scale_bytes);
+        side, my_rank, world, tokens, topk, k, capacity_rows);
+  ES_CUDA_TRY(cudaGetLastError());
+  return ES_B200_OK;
+}
+
+extern "C" int es_b200_ep_unpack_side(const void* side, const int32_t* num_rows_dev, uint8_t* scales, int32_t* meta,
+                                      int k, int64_t capacity_rows, int64_t scale_bytes, void* stream) {
+  using namespace es_b200;
+  ES_REQUIRE(k > 0 && k % 128 == 0 && k <= 16384, "k must align to 128 and be at most 16384");
+  ES_REQUIRE(capacity_rows > 0 && capacity_rows < (int64_t)1 << 31 && scale_bytes > 0, "buffer sizes out of range");
+  ES_REQUIRE(side && num_rows_dev && scales && meta, "null pointer argument");
+  ES_REQUIRE(aligned16(side) && (reinterpret_cast<uintptr_t>(scales) & 3u) == 0 &&
+                 (reinterpret_cast<uintptr_t>(meta) & 7u) == 0,
+             "side must be 16-byte, meta 8-byte and scales 4-byte aligned");
+  int grid = 1;
+  int rc = ep::grid_for(capacity_rows, &grid);
+  if (rc != ES_B200_OK) return rc;
+  ep::unpack_side_kernel<<<grid, ep::THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(side), num_rows_dev, scales, reinterpret_cast<int2*>(meta), k, capacity_rows,
+      scale_bytes);
   ES_CUDA_TRY(cudaGetLastError());
   return ES_B200_OK;
 }

@@ -257,9 +257,9 @@ def moe_forward(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Ten
 
 class FusedExchange:
     """Dispatch and combine of one MoE layer over peer memory (see the module docstring).  One instance per rank holds
-    one symmetric allocation: receive buffers for codes [capacity, H], swizzled scales, return addresses [capacity, 2],
-    and the (token, j) slots [tokens * topk, H] the expert outputs come back to.  `capacity` defaults to the worst
-    case (every pair of every rank routed to this rank)."""
+    one symmetric allocation: receive buffers for codes [capacity, H] and side records (return address, scale position,
+    scale bytes of each row), the (token, j) slots [tokens * topk, H] the expert outputs come back to, the count
+    matrix and the barrier flags.  `capacity` defaults to the worst case (every pair of every rank routed here)."""
 
     def __init__(self, num_experts: int, topk: int, tokens: int, hidden: int, device: torch.device,
                  group: Optional[dist.ProcessGroup] = None, capacity_rows: Optional[int] = None,
@@ -275,7 +275,9 @@ class FusedExchange:
         self.capacity = int(capacity_rows or self.world * tokens * topk)
         self.scale_rows = (self.capacity + 128 * self.e_local + 127) // 128 * 128
         self.scale_bytes = self.scale_rows * (hidden // 32)
-        sizes = [self.capacity * hidden, self.scale_bytes, self.capacity * 8, tokens * topk * hidden * 2, 17 * 4,
+        self._lib = _cabi.load()
+        self.side_bytes = int(self._lib.es_b200_ep_side_record_bytes(hidden))
+        sizes = [self.capacity * hidden, self.capacity * self.side_bytes, 0, tokens * topk * hidden * 2, 17 * 4,
                  self.world * num_experts * 4]
         offs, total = [], 0
         for sz in sizes:
@@ -285,11 +287,12 @@ class FusedExchange:
         self.buf.zero_()
         self.hdl = symm.rendezvous(self.buf, self.group)
         self.codes = self.buf[offs[0]:offs[0] + sizes[0]].view(torch.float8_e4m3fn).view(self.capacity, hidden)
-        self.scales = self.buf[offs[1]:offs[1] + sizes[1]].view(self.scale_rows, hidden // 32)
-        self.meta = self.buf[offs[2]:offs[2] + sizes[2]].view(torch.int32).view(self.capacity, 2)
+        self.side = self.buf[offs[1]:offs[1] + sizes[1]].view(self.capacity, self.side_bytes)
+        self.scales = torch.zeros((self.scale_rows, hidden // 32), dtype=torch.uint8, device=device)   # local
+        self.meta = torch.zeros((self.capacity, 2), dtype=torch.int32, device=device)                  # local
         self.pairs = self.buf[offs[3]:offs[3] + sizes[3]].view(dtype).view(tokens * topk, hidden)
         table = lambda k: (ctypes.c_void_p * self.world)(*[int(p) + offs[k] for p in self.hdl.buffer_ptrs])
-        (self._peer_codes, self._peer_scales, self._peer_meta, self._peer_pairs, self._peer_flags,
+        (self._peer_codes, self._peer_side, _, self._peer_pairs, self._peer_flags,
          self._peer_counts) = (table(k) for k in range(6))
         self.counts_all = self.buf[offs[5]:offs[5] + sizes[5]].view(torch.int32).view(self.world, num_experts)
         pairs = tokens * topk
@@ -299,7 +302,6 @@ class FusedExchange:
                         "dst_scale_offset": torch.empty(pairs, dtype=torch.int64, device=device),
                         "rows": i32(self.e_local), "expert_offsets": i32(self.e_local),
                         "blockscale_offsets": i32(self.e_local), "total_rows": i32(1)}
-        self._lib = _cabi.load()
         self._check = _cabi.check
         self._dtype_code = _cabi.BF16 if dtype == torch.bfloat16 else _cabi.FP16
         self.work = {}
@@ -338,9 +340,12 @@ class FusedExchange:
         s = torch.cuda.current_stream(x.device).cuda_stream
         self._check(self._lib.es_b200_ep_dispatch_quant_push(
             x.data_ptr(), self._dtype_code, plan["dst_rank"].data_ptr(), plan["dst_row"].data_ptr(),
-            plan["dst_scale_offset"].data_ptr(), self._peer_codes, self._peer_scales, self._peer_meta, self.rank,
-            self.world, self.tokens, self.topk, self.hidden, self.capacity, self.scale_bytes, s))
+            plan["dst_scale_offset"].data_ptr(), self._peer_codes, self._peer_side, self.rank, self.world, self.tokens,
+            self.topk, self.hidden, self.capacity, s))
         self.barrier(x.device)                  # all ranks' stores into my buffers are complete and visible
+        self._check(self._lib.es_b200_ep_unpack_side(self.side.data_ptr(), plan["total_rows"].data_ptr(),
+                                                     self.scales.data_ptr(), self.meta.data_ptr(), self.hidden,
+                                                     self.capacity, self.scale_bytes, s))
         return self.codes, self.scales
 
     def combine(self, y: torch.Tensor, plan: dict, topk_weights: torch.Tensor) -> torch.Tensor:

@@ -137,17 +137,21 @@ int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, const uint8_t
  * Expert-parallel exchange over peer memory (one process per GPU; the experts of a layer are spread over the GPUs of a
  * node).  No counterpart in the reference, which has no distributed code: these three calls replace what a caller
  * would otherwise build from an all-to-all, a permutation and es_sm100_mxfp8_blockscaled_grouped_quant
- * (ops.py:40-50) on the way in, and an all-to-all plus a weighted sum on the way out.  The peer_* arrays are HOST
+ * (ops.py:40-50) on the way in, and an all-to-all plus a weighted sum on the way out (the first four calls below;
+ * es_b200_mxfp8_grouped_mm_scatter above fuses the way out into the GEMM).  The peer_* arrays are HOST
  * arrays of `world` device pointers, entry i being GPU i's buffer mapped into this process (peer access enabled;
  * entry my_rank is the local buffer).  The calls only enqueue plain stores to those buffers; the caller orders the
  * GPUs with a barrier after each step.  Destinations out of range are skipped and reported by es_b200_check_status.
  *
  * es_b200_ep_dispatch_quant_push: quantises each of the `tokens` rows of x [tokens, k] once (MXFP8, bit-identical to
  *   the grouped quant) and stores, for each of its topk destinations j (pair = token * topk + j): the codes to row
- *   dst_row[pair] of peer_codes[dst_rank[pair]] ([capacity_rows, k] bytes), the row's scale words to
- *   peer_scales[dst_rank[pair]] + dst_scale_offset[pair] + 512 * (K tile) (dst_scale_offset = byte offset of the row's
- *   word for K tile 0 in the swizzled layout, i.e. blockscale_offset * k/32 + the row's position inside its expert),
- *   and (my_rank, pair) to row dst_row[pair] of peer_meta[dst_rank[pair]] ([capacity_rows, 2] int32).
+ *   dst_row[pair] of peer_codes[dst_rank[pair]] ([capacity_rows, k] bytes), and one side record to row dst_row[pair]
+ *   of peer_side[dst_rank[pair]] ([capacity_rows, es_b200_ep_side_record_bytes(k)] bytes): { int32 my_rank, int32
+ *   pair, int64 dst_scale_offset[pair], k/32 scale bytes }.  dst_scale_offset = byte offset of the row's scale word
+ *   for K tile 0 in the owner's swizzled scale buffer (blockscale_offset * k/32 + the row's position inside its
+ *   expert).
+ * es_b200_ep_unpack_side (local, after the barrier): for rows r < *num_rows_dev of `side`, writes the scale bytes to
+ *   `scales` (swizzled layout, scale_bytes long) and (source GPU, pair) to meta[r] ([capacity_rows, 2] int32).
  * es_b200_ep_combine_push: stores row r < *num_rows_dev of y [capacity_rows, n] (2-byte elements) to row meta[r][1]
  *   of peer_pairs[meta[r][0]] ([pairs_per_rank, n]).
  * es_b200_ep_topk_weighted_sum: out[t, :] = sum_j weights[t, j] * pairs[t * topk + j, :] (fp32 accumulation in j order).
@@ -156,11 +160,13 @@ int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, const uint8_t
  *   waits until all peers have announced theirs (at most five seconds, then it sets a status bit and returns).  Work
  *   enqueued after it on `stream` sees everything the peers stored to this GPU before their matching call.
  */
+int es_b200_ep_side_record_bytes(int k);
 int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const int32_t* dst_rank, const int32_t* dst_row,
                                    const int64_t* dst_scale_offset, const void* const* peer_codes,
-                                   const void* const* peer_scales, const void* const* peer_meta, int my_rank,
-                                   int world, int tokens, int topk, int k, int64_t capacity_rows, int64_t scale_bytes,
-                                   void* stream);
+                                   const void* const* peer_side, int my_rank, int world, int tokens, int topk, int k,
+                                   int64_t capacity_rows, void* stream);
+int es_b200_ep_unpack_side(const void* side, const int32_t* num_rows_dev, uint8_t* scales, int32_t* meta, int k,
+                           int64_t capacity_rows, int64_t scale_bytes, void* stream);
 int es_b200_ep_combine_push(const void* y, const int32_t* meta, const int32_t* num_rows_dev,
                             const void* const* peer_pairs, int world, int64_t capacity_rows, int64_t pairs_per_rank,
                             int n, int elem_bytes, void* stream);
