@@ -132,7 +132,8 @@ dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_
     }
     __syncwarp();                // the record is rewritten by the next row
   }
-  __threadfence_system();      // the stores above are to other GPUs' memory
+  // no fence here: the stores become visible to the peers with the completion of this kernel, and the barrier kernel
+  // that follows on the stream orders them before its flag
 }
 
 // One warp per received row: the side record's scale bytes go to their swizzled position, its return address to the
@@ -192,7 +193,6 @@ combine_push_kernel(const uint4* __restrict__ y, const int2* __restrict__ meta, 
         if (c + j * 32 < row_vec16) dst[c + j * 32] = v[j];
     }
   }
-  __threadfence_system();
 }
 
 template <typename T>

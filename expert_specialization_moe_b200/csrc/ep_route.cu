@@ -77,7 +77,6 @@ publish_kernel(const int* __restrict__ seg_counts, int* __restrict__ seg_base, i
     }
     for (int p = 0; p < world; ++p) static_cast<int*>(counts_all.ptr[p])[my_rank * num_experts + e] = running;
   }
-  __threadfence_system();
 }
 
 __global__ void __launch_bounds__(THREADS)

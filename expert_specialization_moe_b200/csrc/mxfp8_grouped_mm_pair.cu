@@ -414,7 +414,6 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     __syncwarp();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
-  if (scatter.meta != nullptr) __threadfence_system();   // rows may have gone to other GPUs
   if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
 }
 
