@@ -34,10 +34,44 @@ __device__ __forceinline__ __nv_bfloat16 out_from_f32<__nv_bfloat16>(float v) { 
 template <>
 __device__ __forceinline__ __half out_from_f32<__half>(float v) { return __float2half_rn(v); }
 
+// One chunk of 32 accumulator columns (tokens c .. c+31, this warp's 32 n) from registers to global memory through the
+// warp's shared-memory tile.  `dest` is the scatter destination of token c + lane (unused for a dense output).
+template <typename OutT, int TOK>
+__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], int c, int valid, OutT* stage_warp, OutT* dst,
+                                            int64_t ld, int lane, const RowScatter& scatter, int2 dest, int col_off,
+                                            uint32_t* status) {
+  const int part = lane & 3;
+#pragma unroll
+  for (int p = 0; p < 32 / TOK; ++p) {
+#pragma unroll
+    for (int j = 0; j < TOK; ++j) stage_warp[j * 32 + lane] = out_from_f32<OutT>(__uint_as_float(v[p * TOK + j]));
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < TOK / 8; ++it) {
+      const int tok = it * 8 + (lane >> 2);
+      const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
+      const int row = c + p * TOK + tok;
+      if (scatter.meta == nullptr) {
+        if (row < valid) *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
+      } else {
+        const int gpu = __shfl_sync(0xffffffffu, dest.x, p * TOK + tok);
+        const int slot = __shfl_sync(0xffffffffu, dest.y, p * TOK + tok);
+        if (row < valid) {
+          if (gpu >= 0 && gpu < scatter.gpus && slot >= 0 && slot < scatter.slots)
+            *reinterpret_cast<uint4*>(static_cast<OutT*>(scatter.base[gpu]) + (int64_t)slot * ld + col_off + part * 8) = val;
+          else
+            atomicOr(status, ERR_SCATTER_DESTINATION);
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // Drains `n_cols` accumulator columns (a multiple of 16) starting at TMEM address `taddr` (this warp's lane quadrant)
 // and stores the first `valid` of them: column j goes to dst[j * ld + 0..31] (dst = &d[first token][first n of warp]).
 // `release` is called once, right after the last TMEM read has completed (the accumulator may then be overwritten).
-// TOK = tokens per pass through the shared-memory tile (32: 2 KB per warp; 16: 1 KB per warp, two passes per chunk).
+// TOK = tokens per pass through the shared-memory tile (32: 2 KB per warp; 16: 1 KB; 8: 512 bytes).
 // With a scatter map, column j goes to the mapped row of output row `first_row + j`, at column offset `col_off`
 // (`dst` is then unused); `status` is the kernel's error word.
 template <typename OutT, int TOK = 32, class Release>
@@ -48,14 +82,13 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
   // two register sets: the TMEM read of chunk c+1 is in flight while chunk c goes through shared memory
   uint32_t va[32], vb[32];
   ptx::tc_ld_32x32b_x32(taddr, va);
-  const int part = lane & 3;
   for (int c0 = 0; c0 < n_cols; c0 += 64) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int c = c0 + h * 32;
       if (c >= n_cols) break;
       // scatter map: lane l fetches the destination of token c + l now, so that the load's latency hides behind the
-      // TMEM read and the conversions; the store loop below picks it up with a shuffle
+      // TMEM read and the conversions; the store loop picks it up with a shuffle
       int2 dest = make_int2(-1, -1);
       if (scatter.meta != nullptr && do_store && c + lane < valid) dest = scatter.meta[first_row + c + lane];
       ptx::tc_wait_ld();                                    // chunk c is in registers (va if h == 0, vb otherwise)
@@ -66,34 +99,34 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
         release();
       }
       if (do_store) {
-#pragma unroll
-        for (int p = 0; p < 32 / TOK; ++p) {
-#pragma unroll
-          for (int j = 0; j < TOK; ++j)
-            stage_warp[j * 32 + lane] = out_from_f32<OutT>(__uint_as_float(h == 0 ? va[p * TOK + j] : vb[p * TOK + j]));
-          __syncwarp();
-#pragma unroll
-          for (int it = 0; it < TOK / 8; ++it) {
-            const int tok = it * 8 + (lane >> 2);
-            const uint4 val = *reinterpret_cast<const uint4*>(stage_warp + tok * 32 + part * 8);
-            const int row = c + p * TOK + tok;
-            if (scatter.meta == nullptr) {
-              if (row < valid) *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
-            } else {
-              const int gpu = __shfl_sync(0xffffffffu, dest.x, p * TOK + tok);
-              const int slot = __shfl_sync(0xffffffffu, dest.y, p * TOK + tok);
-              if (row < valid) {
-                if (gpu >= 0 && gpu < scatter.gpus && slot >= 0 && slot < scatter.slots)
-                  *reinterpret_cast<uint4*>(static_cast<OutT*>(scatter.base[gpu]) + (int64_t)slot * ld + col_off + part * 8) = val;
-                else
-                  atomicOr(status, ERR_SCATTER_DESTINATION);
-              }
-            }
-          }
-          __syncwarp();
-        }
+        if (h == 0) store_chunk<OutT, TOK>(va, c, valid, stage_warp, dst, ld, lane, scatter, dest, col_off, status);
+        else store_chunk<OutT, TOK>(vb, c, valid, stage_warp, dst, ld, lane, scatter, dest, col_off, status);
       }
     }
+  }
+}
+
+// The same for a warp that shares its lane quadrant with other warps: it takes the 32-column chunks first_chunk,
+// first_chunk + chunk_stride, ... and keeps one register set — the warps of a quadrant hide each other's TMEM
+// latency.  A warp without a chunk only calls `release`.
+template <typename OutT, int TOK, class Release>
+__device__ __forceinline__ void drain_accumulator_shared(uint32_t taddr, int n_cols, int valid, OutT* stage_warp,
+                                                         OutT* dst, int64_t ld, bool do_store, int lane,
+                                                         Release release, const RowScatter& scatter,
+                                                         int64_t first_row, int col_off, uint32_t* status,
+                                                         int first_chunk, int chunk_stride) {
+  if (first_chunk >= n_cols) {
+    release();
+    return;
+  }
+  uint32_t v[32];
+  for (int c = first_chunk; c < n_cols; c += chunk_stride) {
+    int2 dest = make_int2(-1, -1);
+    if (scatter.meta != nullptr && do_store && c + lane < valid) dest = scatter.meta[first_row + c + lane];
+    ptx::tc_ld_32x32b_x32(taddr + c, v);
+    ptx::tc_wait_ld();
+    if (c + chunk_stride >= n_cols) release();
+    if (do_store) store_chunk<OutT, TOK>(v, c, valid, stage_warp, dst, ld, lane, scatter, dest, col_off, status);
   }
 }
 

@@ -16,10 +16,11 @@
 //             the two token sub-tiles, own weight scale atom, the item's token scale atoms); all completion bytes
 //             are credited to the leader CTA's barrier
 //   warp 1    TMEM allocation (both CTAs); in the leader CTA one lane issues sub-tile 0's four tcgen05.mma per K step
-//   warps 2-5 epilogue of accumulator 0 (both CTAs): own 128 accumulator lanes -> bf16/fp16 -> global
-//   warps 6-9 epilogue of accumulator 1, at the same time as warps 2-5
-//   warp 10   leader CTA, one lane: sub-tile 1's four tcgen05.mma per K step
-//   warp 11   leader CTA, one lane: the K step's four tcgen05.cp (scales smem -> TMEM of both CTAs)
+//   warps 2-9   epilogue of accumulator 0 (both CTAs): own 128 accumulator lanes -> bf16/fp16 -> global; two warps
+//               per TMEM lane quadrant take alternate 32-column chunks
+//   warps 10-17 epilogue of accumulator 1, at the same time
+//   warp 18     leader CTA, one lane: sub-tile 1's four tcgen05.mma per K step
+//   warp 19     leader CTA, one lane: the K step's four tcgen05.cp (scales smem -> TMEM of both CTAs)
 //
 // Three issuing lanes instead of one because a tcgen05 instruction costs the thread that issues it ~90 cycles (mma)
 // or ~65 cycles (cp) whatever its size (measured: the K step of a single issuing lane took the same ~1000 cycles with
@@ -38,7 +39,7 @@
 namespace es_b200 {
 namespace mm2 {
 
-constexpr int THREADS = 384;
+constexpr int THREADS = 640;
 constexpr int TILE_N = 128;      // weight rows per CTA (the pair covers 256)
 constexpr int TILE_K = 128;
 constexpr int SUB_TILE = 192;    // token rows per accumulator (MMA N, runtime multiple of 16)
@@ -59,16 +60,18 @@ static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 constexpr uint32_t ERR_PRODUCER = 0x10u, ERR_MMA = 0x20u, ERR_EPILOGUE = 0x40u;
 constexpr uint32_t ERR_SCALE_OFFSET = 0x80u;   // a blockscale offset that is not a multiple of 128 rows
 constexpr uint32_t ERR_SCALE_COPY = 0x100u;
-constexpr int EPI_WARPS = 8;
-constexpr int EPI_TOK = 16;                                // tokens per pass of an epilogue warp's shared-memory tile
-constexpr int EPI_BYTES_PER_WARP = EPI_TOK * 32 * 2;       // 1 KB
+constexpr int EPI_WARPS = 16;                              // per accumulator: 4 lane quadrants x 2 warps
+constexpr int EPI_TOK = 8;                                 // tokens per pass of an epilogue warp's shared-memory tile
+constexpr int EPI_BYTES_PER_WARP = EPI_TOK * 32 * 2;       // 512 bytes
+constexpr int MMA_B_WARP = 2 + EPI_WARPS;                  // 18
+constexpr int COPY_WARP = MMA_B_WARP + 1;                  // 19
 
 struct SharedCtl {
   uint64_t full[STAGES];        // used in the leader CTA only
   uint64_t empty[STAGES];       // 2 arrivals: one commit from each MMA lane
   uint64_t sf_ready[STAGES];    // leader only: the stage's scales are in the TMEM of both CTAs
   uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];       // used in the leader CTA only (8 arrivals: 4 epilogue warps x 2 CTAs)
+  uint64_t tmem_empty[2];       // used in the leader CTA only (16 arrivals: 8 epilogue warps x 2 CTAs)
                                 // index = accumulator (sub-tile 0 / 1)
   uint32_t tmem_base;
   int abort_flag;
@@ -154,7 +157,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
                              int wait_at_start, const __grid_constant__ RowScatter scatter) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 8 x 1 KB, one per epilogue warp
+  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 16 x 512 bytes, one per epilogue warp
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + EPI_WARPS * EPI_BYTES_PER_WARP);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -170,7 +173,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&ctl->tmem_full[a], 1);
-      ptx::mbar_init(&ctl->tmem_empty[a], 8);
+      ptx::mbar_init(&ctl->tmem_empty[a], EPI_WARPS);
     }
     ctl->abort_flag = 0;
 #ifdef ES_PROFILE
@@ -280,7 +283,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       atomicAdd(&g_prof[2 + 4 * rank], (unsigned long long)_acc[2]);
     }
 #endif
-  } else if (warp == 1 || warp == 10) {
+  } else if (warp == 1 || warp == MMA_B_WARP) {
     // ------------------------------------------------------------------ MMA issue (leader CTA): warp 1 issues the
     // MMAs of sub-tile 0 into accumulator 0, warp 10 those of sub-tile 1 into accumulator 1
     if (lane == 0 && rank == 0) {
@@ -346,7 +349,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       if (sub == 0) atomicAdd(&g_prof[12], (unsigned long long)_acc[3]);
 #endif
     }
-  } else if (warp == 11) {
+  } else if (warp == COPY_WARP) {
     // ------------------------------------------------------------------ scale copies (leader CTA, one lane)
     // Token rows 0..383 of the item = scale atoms 0..2: sub-tile 0 reads atoms 0 and 1, sub-tile 1 atoms 1 and 2.
     if (lane == 0 && rank == 0) {
@@ -376,8 +379,11 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs): warps 2..5 drain
     // accumulator 0, warps 6..9 accumulator 1, at the same time
+    // warps 2..9 drain accumulator 0, warps 10..17 accumulator 1; the two warps of a lane quadrant take alternate
+    // 32-column chunks
     const int q = warp & 3;
-    const int sub = (warp - 2) >> 2;
+    const int sub = (warp - 2) >> 3;
+    const int half = ((warp - 2) >> 2) & 1;
     uint32_t full_ph = 0;
     for (int t = pair; t < total_tiles; t += num_pairs) {
       const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
@@ -398,12 +404,14 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + sub * ACC_COLS + ((uint32_t)(q * 32) << 16);
       OutT* dst = d + (int64_t)(ti.row0 + sub * SUB_TILE) * n + (nt * TILE_N + q * 32);
-      drain_accumulator<OutT, EPI_TOK>(taddr, n_mma, valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * (EPI_TOK * 32),
-                                       dst, n, store, lane, [&] {
-                                         ptx::tc_fence_before_sync();
-                                         __syncwarp();
-                                         if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[sub], 0);   // leader's barrier
-                                       }, scatter, ti.row0 + sub * SUB_TILE, nt * TILE_N + q * 32, &g_status);
+      drain_accumulator_shared<OutT, EPI_TOK>(
+          taddr, n_mma, valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * (EPI_TOK * 32), dst, n, store, lane,
+          [&] {
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[sub], 0);   // leader's barrier
+          },
+          scatter, ti.row0 + sub * SUB_TILE, nt * TILE_N + q * 32, &g_status, half * 32, 64);
     }
   }
 
