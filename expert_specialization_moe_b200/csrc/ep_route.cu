@@ -61,21 +61,37 @@ count_kernel(const void* __restrict__ ids, int ids_int64, int pairs, int num_exp
 }
 
 // seg_base[seg][e] = pairs to expert e in segments before seg; this GPU's totals go to row my_rank of every peer's
-// count matrix
+// count matrix.  One block of 1024 threads: the segments are cut into 1024 / E groups (a power of two), thread
+// (group, e) sums its group, a short scan over the groups gives its starting value, a second pass writes the prefixes.
 __global__ void __launch_bounds__(1024)
 publish_kernel(const int* __restrict__ seg_counts, int* __restrict__ seg_base, int num_experts,
                const __grid_constant__ PeerTable counts_all, int my_rank, int world) {
+  __shared__ int group_sum[1024];
   pdl_wait_prior_grid();
   pdl_launch_dependents();
-  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) {
-    int running = 0;
+  int groups = 1;
+  while (groups * 2 * num_experts <= 1024 && groups * 2 <= SEGMENTS) groups *= 2;
+  const int per_group = SEGMENTS / groups;
+  const int g = threadIdx.x / num_experts, e = threadIdx.x - g * num_experts;
+  const bool active = g < groups;
+  int total = 0;
+  if (active) {
 #pragma unroll 8
-    for (int s = 0; s < SEGMENTS; ++s) {
+    for (int s = g * per_group; s < (g + 1) * per_group; ++s) total += seg_counts[(int64_t)s * num_experts + e];
+    group_sum[g * num_experts + e] = total;
+  }
+  __syncthreads();
+  if (active) {
+    int running = 0;
+    for (int h = 0; h < g; ++h) running += group_sum[h * num_experts + e];
+#pragma unroll 8
+    for (int s = g * per_group; s < (g + 1) * per_group; ++s) {
       const int c = seg_counts[(int64_t)s * num_experts + e];
       seg_base[(int64_t)s * num_experts + e] = running;
       running += c;
     }
-    for (int p = 0; p < world; ++p) static_cast<int*>(counts_all.ptr[p])[my_rank * num_experts + e] = running;
+    if (g == groups - 1)
+      for (int p = 0; p < world; ++p) static_cast<int*>(counts_all.ptr[p])[my_rank * num_experts + e] = running;
   }
 }
 
