@@ -34,12 +34,24 @@ __device__ __forceinline__ __nv_bfloat16 out_from_f32<__nv_bfloat16>(float v) { 
 template <>
 __device__ __forceinline__ __half out_from_f32<__half>(float v) { return __float2half_rn(v); }
 
+// Scatter destination of output row `row` as a pointer to the warp's first column in that row, or null (entry out of
+// range: reported; row past the valid ones: silent).
+template <typename OutT>
+__device__ __forceinline__ OutT* scatter_row_ptr(const RowScatter& scatter, int64_t row, bool in_range, int64_t ld,
+                                                 int col_off, uint32_t* status) {
+  if (!in_range) return nullptr;
+  const int2 m = scatter.meta[row];
+  if (m.x >= 0 && m.x < scatter.gpus && m.y >= 0 && m.y < scatter.slots)
+    return static_cast<OutT*>(scatter.base[m.x]) + (int64_t)m.y * ld + col_off;
+  atomicOr(status, ERR_SCATTER_DESTINATION);
+  return nullptr;
+}
+
 // One chunk of 32 accumulator columns (tokens c .. c+31, this warp's 32 n) from registers to global memory through the
-// warp's shared-memory tile.  `dest` is the scatter destination of token c + lane (unused for a dense output).
+// warp's shared-memory tile.  `dest_row` is the scatter destination of token c + lane (unused for a dense output).
 template <typename OutT, int TOK>
 __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], int c, int valid, OutT* stage_warp, OutT* dst,
-                                            int64_t ld, int lane, const RowScatter& scatter, int2 dest, int col_off,
-                                            uint32_t* status) {
+                                            int64_t ld, int lane, const RowScatter& scatter, OutT* dest_row) {
   const int part = lane & 3;
 #pragma unroll
   for (int p = 0; p < 32 / TOK; ++p) {
@@ -54,14 +66,9 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], int c, int 
       if (scatter.meta == nullptr) {
         if (row < valid) *reinterpret_cast<uint4*>(dst + (int64_t)row * ld + part * 8) = val;
       } else {
-        const int gpu = __shfl_sync(0xffffffffu, dest.x, p * TOK + tok);
-        const int slot = __shfl_sync(0xffffffffu, dest.y, p * TOK + tok);
-        if (row < valid) {
-          if (gpu >= 0 && gpu < scatter.gpus && slot >= 0 && slot < scatter.slots)
-            *reinterpret_cast<uint4*>(static_cast<OutT*>(scatter.base[gpu]) + (int64_t)slot * ld + col_off + part * 8) = val;
-          else
-            atomicOr(status, ERR_SCATTER_DESTINATION);
-        }
+        const unsigned long long bits = reinterpret_cast<unsigned long long>(dest_row);
+        OutT* out = reinterpret_cast<OutT*>(__shfl_sync(0xffffffffu, bits, p * TOK + tok));
+        if (out != nullptr) *reinterpret_cast<uint4*>(out + part * 8) = val;
       }
     }
     __syncwarp();
@@ -89,8 +96,9 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
       if (c >= n_cols) break;
       // scatter map: lane l fetches the destination of token c + l now, so that the load's latency hides behind the
       // TMEM read and the conversions; the store loop picks it up with a shuffle
-      int2 dest = make_int2(-1, -1);
-      if (scatter.meta != nullptr && do_store && c + lane < valid) dest = scatter.meta[first_row + c + lane];
+      OutT* dest = nullptr;
+      if (scatter.meta != nullptr && do_store)
+        dest = scatter_row_ptr<OutT>(scatter, first_row + c + lane, c + lane < valid, ld, col_off, status);
       ptx::tc_wait_ld();                                    // chunk c is in registers (va if h == 0, vb otherwise)
       const bool more = c + 32 < n_cols;
       if (more) {
@@ -99,8 +107,8 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
         release();
       }
       if (do_store) {
-        if (h == 0) store_chunk<OutT, TOK>(va, c, valid, stage_warp, dst, ld, lane, scatter, dest, col_off, status);
-        else store_chunk<OutT, TOK>(vb, c, valid, stage_warp, dst, ld, lane, scatter, dest, col_off, status);
+        if (h == 0) store_chunk<OutT, TOK>(va, c, valid, stage_warp, dst, ld, lane, scatter, dest);
+        else store_chunk<OutT, TOK>(vb, c, valid, stage_warp, dst, ld, lane, scatter, dest);
       }
     }
   }
@@ -121,12 +129,13 @@ __device__ __forceinline__ void drain_accumulator_shared(uint32_t taddr, int n_c
   }
   uint32_t v[32];
   for (int c = first_chunk; c < n_cols; c += chunk_stride) {
-    int2 dest = make_int2(-1, -1);
-    if (scatter.meta != nullptr && do_store && c + lane < valid) dest = scatter.meta[first_row + c + lane];
+    OutT* dest = nullptr;
+    if (scatter.meta != nullptr && do_store)
+      dest = scatter_row_ptr<OutT>(scatter, first_row + c + lane, c + lane < valid, ld, col_off, status);
     ptx::tc_ld_32x32b_x32(taddr + c, v);
     ptx::tc_wait_ld();
     if (c + chunk_stride >= n_cols) release();
-    if (do_store) store_chunk<OutT, TOK>(v, c, valid, stage_warp, dst, ld, lane, scatter, dest, col_off, status);
+    if (do_store) store_chunk<OutT, TOK>(v, c, valid, stage_warp, dst, ld, lane, scatter, dest);
   }
 }
 
