@@ -49,6 +49,7 @@ WORKLOADS = {
                                    "e4m3 codes + swizzled UE8M0 scales"),
     "qwen3_ep": (128, 0, 0, 0, "Qwen3-30B-A3B-shaped MoE layer with expert parallelism (N >= 2), dispatch / combine "
                                "over peer memory (FusedExchange)"),
+    "qwen3_ep_pipelined": (128, 0, 0, 0, "the qwen3_ep layer as two half-batches on two streams (PipelinedExchange)"),
     "qwen3_ep_nccl": (128, 0, 0, 0, "Qwen3-30B-A3B-shaped MoE layer with expert parallelism (N >= 2), NCCL all-to-all "
                                     "dispatch / combine"),
     # the reference's own published benchmark (benchmark/benchmark_es_fp8_blockwise_moe.py: uniform-random top-8
@@ -290,11 +291,14 @@ def bench_ep_layer(args, device, rank, world, dist):
     p = torch.softmax(torch.randn((tokens, E), generator=g, device=device), -1)
     wts, ids = torch.topk(p, topk, dim=-1)
     wts = (wts / wts.sum(-1, keepdim=True)).to(torch.float32)
-    fused = args.workload == "qwen3_ep"
+    fused = args.workload in ("qwen3_ep", "qwen3_ep_pipelined")
     if fused:
         # capacity: 2x the balanced share is ample for softmax-of-N(0,1) routing; overflow would be reported as an
         # out-of-range destination by es_b200_check_status below
-        fx = ep.FusedExchange(E, topk, tokens, H, device, capacity_rows=2 * tokens * topk)
+        if args.workload == "qwen3_ep_pipelined":
+            fx = ep.PipelinedExchange(E, topk, tokens, H, device, capacity_rows=2 * tokens * topk)
+        else:
+            fx = ep.FusedExchange(E, topk, tokens, H, device, capacity_rows=2 * tokens * topk)
         step = lambda: fx.forward(x, ids, wts, shard)
     else:
         step = lambda: ep.moe_forward(x, ids, wts, E, shard.forward)
@@ -334,12 +338,14 @@ def bench_ep_layer(args, device, rank, world, dist):
                 "vs_baseline": None, "dtype": "mxfp8_e4m3", "data": "synthetic",
                 "config": {"workload": "Qwen3-30B-A3B-shaped MoE layer: E=128, top-8, hidden 2048, intermediate 768, "
                                        "16384 tokens per GPU, " + ("dispatch/combine as peer-memory stores fused with "
-                                       "the quantisation (FusedExchange)" if fused else "NCCL all-to-all dispatch/combine"),
+                                       "the quantisation (FusedExchange)" + (", two half-batches on two streams"
+                                       if args.workload == "qwen3_ep_pipelined" else "") if fused
+                                       else "NCCL all-to-all dispatch/combine"),
                            "experts_per_gpu": e_local},
                 "clocks": clocks, "device_status": status,
                 # ours per step: dispatch-quant-push, 2 barriers, up to 3 + 3 GEMM bucket kernels, silu-quant,
                 # combine-push, weighted sum (fused) / 2 quant kernels + GEMMs (all-to-all path)
-                "gpu_launches": args.steps * (12 if fused else 8)}
+                "gpu_launches": args.steps * ((26 if args.workload == "qwen3_ep_pipelined" else 13) if fused else 8)}
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()

@@ -49,7 +49,6 @@ __device__ __forceinline__ void st_8B(void* p, uint2 v) {
 // Side record of a received row: { int32 source GPU, int32 pair index, int64 byte offset of the row's scale word for
 // K tile 0 in the owner's swizzled scale buffer, k/32 scale bytes }, padded to a multiple of 16 bytes.
 __host__ __device__ __forceinline__ int side_record_bytes(int k) { return 16 + (((k >> 5) + 15) & ~15); }
-constexpr int MAX_SIDE_BYTES = 16 + 512;        // k <= 16384
 
 // One warp per token row.  Per pass a lane holds 4 x 8 elements (1024 elements per warp); the codes of the pass stay
 // in registers while they are stored to each of the row's top-k destinations, the scale words collect in a per-warp
@@ -60,13 +59,15 @@ dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_
                            const long long* __restrict__ dst_sf_offset, const __grid_constant__ PeerTable codes,
                            const __grid_constant__ PeerTable side, int my_rank, int world, int tokens, int topk, int k,
                            long long capacity_rows) {
-  __shared__ __align__(16) uint8_t side_s[THREADS / 32][MAX_SIDE_BYTES];
+  // one side record per warp; dynamic, so that the kernel's footprint stays small enough to share an SM with a
+  // grouped GEMM CTA of another stream
+  extern __shared__ __align__(16) uint8_t side_s[];
   pdl_wait_prior_grid();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int warps_per_grid = gridDim.x * (THREADS / 32);
   const int side_bytes = side_record_bytes(k);
-  uint8_t* rec = side_s[warp];
+  uint8_t* rec = side_s + warp * side_bytes;
   for (int t = blockIdx.x * (THREADS / 32) + warp; t < tokens; t += warps_per_grid) {
     // lane j < topk holds destination j; bad destinations are dropped here, once
     int my_rank_j = -1, my_row_j = 0;
@@ -337,12 +338,13 @@ extern "C" int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const 
   rc = ep::grid_for(tokens, &grid);
   if (rc != ES_B200_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t side_smem = (size_t)(ep::THREADS / 32) * ep::side_record_bytes(k);
   if (x_dtype == ES_B200_BF16)
-    ep::dispatch_quant_push_kernel<__nv_bfloat16><<<grid, ep::THREADS, 0, s>>>(
+    ep::dispatch_quant_push_kernel<__nv_bfloat16><<<grid, ep::THREADS, side_smem, s>>>(
         static_cast<const __nv_bfloat16*>(x), dst_rank, dst_row, reinterpret_cast<const long long*>(dst_scale_offset),
         codes, side, my_rank, world, tokens, topk, k, capacity_rows);
   else
-    ep::dispatch_quant_push_kernel<__half><<<grid, ep::THREADS, 0, s>>>(
+    ep::dispatch_quant_push_kernel<__half><<<grid, ep::THREADS, side_smem, s>>>(
         static_cast<const __half*>(x), dst_rank, dst_row, reinterpret_cast<const long long*>(dst_scale_offset), codes,
         side, my_rank, world, tokens, topk, k, capacity_rows);
   ES_CUDA_TRY(cudaGetLastError());

@@ -381,3 +381,28 @@ class FusedExchange:
         if fuse_combine:
             return self.reduce(topk_weights)
         return self.combine(y, plan, topk_weights)
+
+
+class PipelinedExchange:
+    """The same layer on two halves of the token batch, each with its own FusedExchange and CUDA stream, so that one
+    half's NVLink-bound steps (dispatch, the down GEMM's scatter epilogue) can run while the other half computes."""
+
+    def __init__(self, num_experts: int, topk: int, tokens: int, hidden: int, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None, capacity_rows: Optional[int] = None):
+        assert tokens % 2 == 0
+        self.half = tokens // 2
+        cap = None if capacity_rows is None else capacity_rows // 2
+        self.parts = [FusedExchange(num_experts, topk, self.half, hidden, device, group, cap) for _ in range(2)]
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(2)]
+
+    def forward(self, x, topk_ids, topk_weights, shard: ExpertShard):
+        cur = torch.cuda.current_stream(x.device)
+        outs = []
+        for i, (fx, st) in enumerate(zip(self.parts, self.streams)):
+            lo, hi = i * self.half, (i + 1) * self.half
+            st.wait_stream(cur)
+            with torch.cuda.stream(st):
+                outs.append(fx.forward(x[lo:hi], topk_ids[lo:hi].contiguous(), topk_weights[lo:hi], shard))
+        for st in self.streams:
+            cur.wait_stream(st)
+        return torch.cat(outs, 0)

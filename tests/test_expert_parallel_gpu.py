@@ -124,6 +124,11 @@ def _worker_fused(rank, world, port, q):
                 if fuse:
                     assert torch.equal(out, out_unfused), "fused and unfused combine differ"
                 out_unfused = out
+        # the same layer as two half-batches on two streams: per-row results do not depend on the batching
+        px = ep.PipelinedExchange(E, topk, tokens, H, dev)
+        out_p = px.forward(x, ids, wts, shard)
+        torch.cuda.synchronize()
+        assert torch.equal(out_p, out), "pipelined and single-stream exchange differ"
         raw = ctypes.c_uint32(0)
         rc = _cabi.load().es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
         q.put((rank, worst if rc == 0 else float("inf"), None))
