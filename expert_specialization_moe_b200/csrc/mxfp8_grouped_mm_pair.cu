@@ -217,7 +217,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (warp 0 of each CTA)
-    // The whole warp walks the work list; per K step lanes 0..4 each issue ONE of the stage's loads in the same
+    // The whole warp walks the work list; per K step lanes 0..6 each issue ONE of the stage's loads in the same
     // instruction (a TMA issue costs the issuing thread ~80 cycles, five in a row would be a third of a stage time).
     int s = 0;
     uint32_t ph = 0;
@@ -377,9 +377,8 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (both CTAs): warps 2..5 drain
-    // accumulator 0, warps 6..9 accumulator 1, at the same time
-    // warps 2..9 drain accumulator 0, warps 10..17 accumulator 1; the two warps of a lane quadrant take alternate
+    // ------------------------------------------------------------------ epilogue (both CTAs), both accumulators at
+    // the same time: warps 2..9 drain accumulator 0, warps 10..17 accumulator 1; the two warps of a lane quadrant take alternate
     // 32-column chunks
     const int q = warp & 3;
     const int sub = (warp - 2) >> 3;
