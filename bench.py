@@ -13,8 +13,11 @@ es_sm100_mxfp8_blockscaled_grouped_mm over the whole batch.  With N GPUs the exp
 Prints ONE JSON line (rank 0).  `value` is the device-timed throughput with operands resident in HBM; `e2e` is the same
 metric through the public op with the activations, their scales and the problem list copied from pinned host memory and
 the output copied back inside the timed region (weights are model state and stay resident).
-`--impl reference` times the CPU dequant+matmul path (the reference's torch path restated in oracle/) on a bounded
-sample of the same workload.
+`--impl reference` on one GPU runs the reference's own SM100 kernels (the unmodified reference sources built by
+oracle/build_ref.sh into oracle/_ref/, called through the reference's torch ops) on the same workload and prints the
+same line; where that library is absent (it never travels to a multi-GPU call: its kernel issues cluster-multicast
+loads) the arm falls back to the CPU dequant+matmul path (the reference's torch path restated in oracle/) on a
+bounded sample of the workload and says so in `reference_kind`.
 """
 from __future__ import annotations
 
@@ -59,6 +62,13 @@ WORKLOADS = {
                                                 "benchmark: E=256, batch 512 x top-8 uniform-random routing, n=512, k=7168"),
     "blockwise_down": (256, 4096, 7168, 256, "FP8-blockwise grouped GEMM, DeepSeek-R1 down TP8 of the reference's "
                                              "benchmark: E=256, batch 512 x top-8 uniform-random routing, n=7168, k=256"),
+    # the reference's own SM100 benchmark (benchmark/benchmark_sm100_mxfp8_blockscaled_moe.py:17-33,153-166): per-expert
+    # row counts drawn 70 % from [1, 32], 15 % from [32, 64], 10 % from [64, 128], 5 % from [128, 1024]
+    "ref_dist": (256, None, 512, 7168, "MXFP8 grouped GEMM on the reference's SM100 benchmark: DeepSeek-R1 gate_up TP8 "
+                                       "(n=512, k=7168, E=256), row counts 70/15/10/5 % from 1-32/32-64/64-128/128-1024"),
+    "ref_dist_ep8": (32, None, 4096, 7168, "MXFP8 grouped GEMM on the reference's SM100 benchmark: DeepSeek-R1 gate_up "
+                                           "EP8 decode (n=4096, k=7168, E=32), row counts 70/15/10/5 % from "
+                                           "1-32/32-64/64-128/128-1024"),
     "quant_small": (64, 8192, 0, 7168, "grouped MXFP8 quantisation at 1/4 scale for profiler captures: bf16 "
                                        "[8192, 7168], E=64"),
 }
@@ -72,6 +82,36 @@ def zipf_counts(T, E, alpha=1.2, seed=0):
     counts = rng.multinomial(T, p)
     rng.shuffle(counts)
     return counts.astype(np.int64)
+
+
+def ref_dist_counts(E, seed=1):
+    """Row counts with the distribution of the reference's SM100 benchmark (its generator draws a class per expert:
+    70 % 1-32 rows, 15 % 32-64, 10 % 64-128, 5 % 128-1024)."""
+    rng = np.random.default_rng(seed)
+    u = rng.random(E)
+    lo = np.where(u <= 0.7, 1, np.where(u <= 0.85, 32, np.where(u <= 0.95, 64, 128)))
+    hi = np.where(u <= 0.7, 32, np.where(u <= 0.85, 64, np.where(u <= 0.95, 128, 1024)))
+    return rng.integers(lo, hi + 1).astype(np.int64)
+
+
+def workload_counts(name):
+    E, T, N, K, _ = WORKLOADS[name]
+    if name == "heavy":
+        return np.full(E, T // E, dtype=np.int64)
+    if name.startswith("ref_dist"):
+        return ref_dist_counts(E)
+    return zipf_counts(T, E, 1.2, 0)
+
+
+REF_LIB = ROOT / "oracle" / "_ref" / "libes_reference.so"
+
+
+def reference_ops():
+    """torch ops of the reference's own SM100 build (oracle/_ref), or None where that library is absent."""
+    if not REF_LIB.exists():
+        return None
+    torch.ops.load_library(str(REF_LIB))
+    return torch.ops.expert_specialization
 
 
 def align128(x):
@@ -183,10 +223,11 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------------------------------
-def build_device_workload(counts, N, K, device, seed):
-    """Quantised operands resident on `device`, produced with this library's own grouped quant op (bit-identical to
-    the reference's): activations N(0,1), weights N(0,0.02), both bf16 -> e4m3 + UE8M0."""
-    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
+def build_device_workload(counts, N, K, device, seed, quant=None):
+    """Quantised operands resident on `device`, produced with the grouped quant op (this library's, bit-identical to
+    the reference's, unless `quant` is given): activations N(0,1), weights N(0,0.02), both bf16 -> e4m3 + UE8M0."""
+    if quant is None:
+        from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
     E = len(counts)
     T = int(counts.sum())
     ps, eo, bo, sfa_rows = offsets(counts, N, K)
@@ -330,6 +371,7 @@ def bench_ep_layer(args, device, rank, world, dist):
     st = torch.tensor([int(raw.value)], dtype=torch.int64, device=device)
     dist.all_reduce(st, op=dist.ReduceOp.MAX)
     status = int(st[0])
+    line = None
     if rank == 0:
         flops = 2.0 * tokens * topk * world * (2 * I * H + H * I)
         line = {"metric": "MoE layer (expert parallel) grouped-GEMM TFLOPS incl. dispatch/combine",
@@ -345,15 +387,18 @@ def bench_ep_layer(args, device, rank, world, dist):
                 "clocks": clocks, "device_status": status,
                 # ours per step: dispatch-quant-push, 2 barriers, up to 3 + 3 GEMM bucket kernels, silu-quant,
                 # combine-push, weighted sum (fused) / 2 quant kernels + GEMMs (all-to-all path)
-                "gpu_launches": args.steps * ((26 if args.workload == "qwen3_ep_pipelined" else 13) if fused else 8)}
-        print(json.dumps(line))
-    dist.barrier()
-    dist.destroy_process_group()
+                "gpu_launches": args.steps * ((30 if args.workload == "qwen3_ep_pipelined" else 15) if fused else 10)}
+    del shard, x
+    torch.cuda.empty_cache()
+    return line
 
 
-def bench_quant(args, E, T, K, desc, device, rank, world, dist):
-    """Grouped quant alone; with N GPUs each rank quantises its own E/N experts' rows (no collective)."""
-    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
+def bench_quant(args, E, T, K, desc, device, rank, world, dist, quant=None):
+    """Grouped quant alone; with N GPUs each rank quantises its own E/N experts' rows (no collective).  `quant`: the
+    reference's op for the reference arm."""
+    is_reference = quant is not None
+    if quant is None:
+        from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
     counts_all = zipf_counts(T, E, 1.2, 0)
     counts = counts_all[rank * (E // world):(rank + 1) * (E // world)]
     Tl = int(counts.sum())
@@ -404,6 +449,10 @@ def bench_quant(args, E, T, K, desc, device, rank, world, dist):
                              "traffic": read_traffic(f"{args.workload}_n{world}"), "peak_kind": peak_kind, "algorithmic_bytes": abytes_local,
                              "kernel": "mxfp8_group_quant_kernel", "kernel_ms": ms},
                 "clocks": clocks, "gpu_launches": args.steps}
+        if is_reference:
+            line["impl"] = "reference"
+            line["reference_kind"] = "gpu_kernel: the reference's own mxfp8_group_quant kernel (oracle/_ref)"
+            line["roofline"]["kernel"] = "reference mxfp8_group_quant"
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()
@@ -519,98 +568,42 @@ def bench_blockwise(args, E, T, N, K, desc, device, rank, world, dist):
 
 
 # ---------------------------------------------------------------------------------------------------------------------
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
-    ap.add_argument("--cpu-budget", type=float, default=20.0, help="seconds of CPU work for the cpu_baseline sample")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--placement", default="contiguous", choices=["contiguous", "balanced"],
-                    help="expert-to-GPU placement for N > 1: contiguous blocks of E/N experts, or E/N experts per GPU "
-                         "chosen greedily (largest first) so that routed rows are balanced")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+def place_experts(counts_all, world, placement, N, K):
+    """Experts (and their row counts) of every rank.  Returns (list of count arrays, note).
+    contiguous: experts [r*E/G, (r+1)*E/G).  balanced: E/G experts per rank, largest first to the least-loaded rank.
+    load_balanced: what an expert-parallel deployment derives from load statistics — an expert with more rows than
+    one rank's fair share is REPLICATED (weights on several ranks, its rows split evenly between the replicas), then
+    every (replica of an) expert goes, most expensive first, to the rank with the least estimated time, where an
+    expert costs max(its weight bytes at HBM speed, its FLOPs at tensor speed)."""
+    E = len(counts_all)
+    per = E // world
+    if placement == "contiguous" or world == 1:
+        return [counts_all[r * per:(r + 1) * per] for r in range(world)], "contiguous blocks of E/N experts"
+    if placement == "balanced":
+        return shard_counts(counts_all, world, "balanced"), "E/N experts per rank, greedy by rows"
+    fair = max(1, int(counts_all.sum()) // world)
+    virtual, replicated = [], 0
+    for m in counts_all:
+        m = int(m)
+        parts = max(1, -(-m // fair)) if m > fair else 1
+        replicated += parts > 1
+        base, extra = divmod(m, parts)
+        virtual += [base + (1 if i < extra else 0) for i in range(parts)]
+    cost = lambda m: max(N * K * (1 + 1 / 32) / 6.2e12, 2.0 * m * N * K / 2.4e15) if m > 0 else 0.0
+    load = [0.0] * world
+    owned = [[] for _ in range(world)]
+    for m in sorted(virtual, key=lambda m: -cost(m)):
+        r = min(range(world), key=lambda i: (load[i], len(owned[i])))
+        owned[r].append(m); load[r] += cost(m)
+    width = max(len(o) for o in owned)
+    shards = [np.array(sorted(o, reverse=True) + [0] * (width - len(o)), dtype=np.int64) for o in owned]
+    return shards, (f"load-balanced: {replicated} expert(s) with more rows than a rank's fair share replicated "
+                    f"(rows split between the replicas), experts placed by estimated time; {width} expert slots per rank")
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    E, T, N, K, desc = WORKLOADS[args.workload]
-    counts_all = zipf_counts(T, E, 1.2, 0) if args.workload != "heavy" else np.full(E, T // E, dtype=np.int64)
-    metric = "MoE-layer grouped-GEMM TFLOPS"
-    config = {"workload": desc, "experts_per_gpu": E // max(world, 1), "placement": "contiguous",
-              "l2": "inputs larger than L2 (weights %.2f GB per GPU), no flush" % ((E // max(world, 1)) * N * K / 1e9),
-              "out_dtype": "bf16"}
 
-    if args.impl == "reference":
-        # the reference's CPU path, bounded sample per step; rank 0 only
-        if rank != 0:
-            return
-        if args.workload.startswith("blockwise"):
-            return reference_blockwise(args, E, T, N, K, desc)
-        rates = []
-        cores = os.cpu_count() or 1
-        # the whole run (warm-up + steps) is kept to about two minutes: each step times one pass over a sample sized
-        # for total / (steps + warm-up) seconds at ~0.2 TFLOP/s
-        per_step_budget = min(args.cpu_budget, max(0.25, 100.0 / max(1, args.steps + args.warmup)))
-        sample = CpuReferenceSample(counts_all, N, K, seed=100, max_flops=per_step_budget * 0.2e12)
-        sdesc = ""
-        for i in range(args.warmup + args.steps):
-            r, cores, secs = sample.run()
-            if i >= args.warmup:
-                rates.append(r)
-                sdesc = sample.describe(secs)
-        v = float(np.mean(rates)) if rates else 0.0
-        flops_total = 2.0 * T * N * K
-        line = {
-            "impl": "reference", "metric": metric, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": flops_total / (v * 1e12) * 1e3 if v else None,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp8_e4m3",
-            "data": "synthetic", "config": config,
-            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sdesc},
-            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0,
-        }
-        print(json.dumps(line))
-        return
-
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py --impl ours needs a CUDA device: the library has no CPU fallback")
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-
-    if args.workload.startswith("quant"):
-        return bench_quant(args, E, T, K, desc, device, rank, world, dist)
-    if args.workload.startswith("qwen3_ep"):
-        if dist is None:                         # one GPU: a process group of one, all experts local
-            import socket
-            import torch.distributed as dist
-            with socket.socket() as sock:
-                sock.bind(("127.0.0.1", 0))
-                port = sock.getsockname()[1]
-            dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
-                                    device_id=device)
-        return bench_ep_layer(args, device, rank, world, dist)
-    if args.workload.startswith("blockwise"):
-        return bench_blockwise(args, E, T, N, K, desc, device, rank, world, dist)
-
-    # expert-parallel shard: E/world experts per rank
-    assert E % world == 0
-    counts = shard_counts(counts_all, world, args.placement)[rank]
-    config["placement"] = args.placement
-    wl = build_device_workload(counts, N, K, device, seed=1000 + rank)
-    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_mm as grouped_mm
-    from expert_specialization_moe_b200 import _cabi
-
+def run_gemm_arm(args, wl, grouped_mm, counts, N, K, device, rank, world, dist, local_rank):
+    """Times args.steps calls of `grouped_mm` on the resident workload, then the same call end to end with host
+    buffers.  Returns (elapsed_ms, my_ms, e2e tuple or None, clocks, host_us_per_call)."""
     def step():
         grouped_mm(wl["d"], wl["a"], wl["b"], wl["sfa"], wl["sfb"], wl["ps"], wl["eo"], wl["bo"])
 
@@ -634,14 +627,15 @@ def main():
     barrier()
     elapsed_ms = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else None
-    lib = _cabi.load()
-    import ctypes
-    raw = ctypes.c_uint32(0)
-    rc = lib.es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
-    if rc != 0:
-        raise SystemExit(f"device-side status {raw.value:#x}: a bounded wait gave up; the timing is invalid")
 
-    # ---- end to end through the public op with host buffers
+    # host time of one call (argument checks, tensor maps, launches): 50 calls enqueued back to back, no sync inside
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    for _ in range(50):
+        step()
+    host_us = (time.perf_counter() - t0) / 50 * 1e6
+    torch.cuda.synchronize(device)
+
     e2e = None
     if not args.no_e2e:
         # Pinned host buffers; per step: H2D of the activations (e4m3 codes + scales) and the problem list, the op, D2H of
@@ -709,6 +703,173 @@ def main():
         h2d = a_h.numel() + sfa_h.numel() + 4 * (ps_h.numel() + eo_h.numel() + bo_h.numel())
         d2h = d_h[0].numel() * d_h[0].element_size()
         e2e = (e2e_ms, h2d, d2h)
+    return elapsed_ms, float(ev0.elapsed_time(ev1)) / args.steps, e2e, clocks, host_us
+
+
+def compare_with_reference_kernel(wl, ours, ref_mm, device, repeats=5, steps=20):
+    """Outside every timed region, one GPU only: this library's call and the reference's own SM100 kernel on the same
+    resident operands, interleaved (ours, reference, ours, ...), `repeats` x `steps` calls each; medians."""
+    d_ref = torch.zeros_like(wl["d"])
+    ref = lambda: ref_mm(wl["a"], wl["b"], wl["sfa"], wl["sfb"], d_ref, wl["ps"], wl["eo"], wl["bo"])
+    mine = lambda: ours(wl["d"], wl["a"], wl["b"], wl["sfa"], wl["sfb"], wl["ps"], wl["eo"], wl["bo"])
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / steps
+
+    for _ in range(3):
+        ref(); mine()
+    torch.cuda.synchronize(device)
+    t_ours, t_ref = [], []
+    for _ in range(repeats):
+        t_ours.append(timed(mine))
+        t_ref.append(timed(ref))
+    same = float((wl["d"].view(torch.int16) == d_ref.view(torch.int16)).float().mean())
+    mo, mr = float(np.median(t_ours)), float(np.median(t_ref))
+    return {"ms_per_step": mr, "ours_ms_per_step": mo, "ratio": mr / mo, "bit_identical_fraction": same,
+            "how": f"interleaved, {repeats} x {steps} calls each, medians; reference = its own SM100 CUTLASS kernel "
+                   f"built from its sources (oracle/_ref)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gate_up", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-budget", type=float, default=20.0, help="seconds of CPU work for the cpu_baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true", help="skip the side-by-side run of the reference kernel")
+    ap.add_argument("--reference-cpu", action="store_true", help="--impl reference: time the CPU port even on one GPU")
+    ap.add_argument("--placement", default=None, choices=["contiguous", "balanced", "load_balanced"],
+                    help="expert-to-GPU placement for N > 1 (default load_balanced): contiguous blocks of E/N experts; "
+                         "E/N experts per GPU chosen greedily by rows; or load-aware with the hottest expert "
+                         "replicated (see place_experts)")
+    ap.add_argument("--ep-layer-steps", type=int, default=10,
+                    help="N > 1, default workload: steps of the expert-parallel layer run after the headline (0 = skip)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    E, T, N, K, desc = WORKLOADS[args.workload]
+    counts_all = workload_counts(args.workload)
+    if T is None:
+        T = int(counts_all.sum())
+    placement = args.placement or ("load_balanced" if world > 1 else "contiguous")
+    metric = "MoE-layer grouped-GEMM TFLOPS"
+    config = {"workload": desc, "experts_per_gpu": E // max(world, 1), "placement": placement,
+              "l2": "inputs larger than L2 (weights %.2f GB per GPU), no flush" % ((E // max(world, 1)) * N * K / 1e9),
+              "out_dtype": "bf16"}
+    gemm_workload = not (args.workload.startswith("quant") or args.workload.startswith("qwen3_ep")
+                         or args.workload.startswith("blockwise"))
+
+    ref = None
+    if args.impl == "reference":
+        # One GPU and the reference's own build present: its SM100 kernels, through its torch ops.  Otherwise the CPU
+        # restatement of its torch dequant-matmul path on a bounded sample (rank 0 only).
+        if (world == 1 and not args.reference_cpu and torch.cuda.is_available()
+                and (gemm_workload or args.workload.startswith("quant"))):
+            ref = reference_ops()
+        if ref is None:
+            if rank != 0:
+                return
+            if args.workload.startswith("blockwise"):
+                return reference_blockwise(args, E, T, N, K, desc)
+            rates = []
+            cores = os.cpu_count() or 1
+            # the whole run (warm-up + steps) is kept to about two minutes: each step times one pass over a sample sized
+            # for total / (steps + warm-up) seconds at ~0.2 TFLOP/s
+            per_step_budget = min(args.cpu_budget, max(0.25, 100.0 / max(1, args.steps + args.warmup)))
+            sample = CpuReferenceSample(counts_all, N, K, seed=100, max_flops=per_step_budget * 0.2e12)
+            sdesc = ""
+            for i in range(args.warmup + args.steps):
+                r, cores, secs = sample.run()
+                if i >= args.warmup:
+                    rates.append(r)
+                    sdesc = sample.describe(secs)
+            v = float(np.mean(rates)) if rates else 0.0
+            flops_total = 2.0 * T * N * K
+            line = {
+                "impl": "reference", "reference_kind": "cpu_port: the reference's torch dequant + per-expert matmul "
+                "path restated (oracle/), host cores; the reference's own SM100 build is not on this box",
+                "metric": metric, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": flops_total / (v * 1e12) * 1e3 if v else None,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "mxfp8_e4m3",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sdesc},
+                "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0,
+            }
+            print(json.dumps(line))
+            return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+
+    if args.workload.startswith("quant"):
+        return bench_quant(args, E, T, K, desc, device, rank, world, dist,
+                           quant=ref.es_sm100_mxfp8_blockscaled_grouped_quant if ref is not None else None)
+    if args.workload.startswith("qwen3_ep"):
+        if dist is None:                         # one GPU: a process group of one, all experts local
+            import socket
+            import torch.distributed as dist
+            with socket.socket() as sock:
+                sock.bind(("127.0.0.1", 0))
+                port = sock.getsockname()[1]
+            dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1,
+                                    device_id=device)
+        line = bench_ep_layer(args, device, rank, world, dist)
+        if rank == 0:
+            print(json.dumps(line))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+    if args.workload.startswith("blockwise"):
+        return bench_blockwise(args, E, T, N, K, desc, device, rank, world, dist)
+
+    # expert-parallel shard
+    assert E % world == 0
+    shards, placement_note = place_experts(counts_all, world, placement, N, K)
+    counts = shards[rank]
+    config["placement_note"] = placement_note
+    config["experts_per_gpu"] = int(len(counts))
+    config["l2"] = "inputs larger than L2 (weights %.2f GB per GPU), no flush" % (int((counts > 0).sum()) * N * K / 1e9)
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_mm as our_mm
+    from expert_specialization_moe_b200 import _cabi
+    if ref is not None:
+        wl = build_device_workload(counts, N, K, device, seed=1000 + rank,
+                                   quant=ref.es_sm100_mxfp8_blockscaled_grouped_quant)
+        grouped_mm = lambda d, a, b, sfa, sfb, ps, eo, bo: ref.es_sm100_mxfp8_blockscaled_grouped_mm(
+            a, b, sfa, sfb, d, ps, eo, bo)
+    else:
+        wl = build_device_workload(counts, N, K, device, seed=1000 + rank)
+        grouped_mm = our_mm
+
+    elapsed_ms, my_ms, e2e, clocks, host_us = run_gemm_arm(args, wl, grouped_mm, counts, N, K, device, rank, world,
+                                                           dist, local_rank)
+    if ref is None:
+        import ctypes
+        raw = ctypes.c_uint32(0)
+        rc = _cabi.load().es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
+        if rc != 0:
+            raise SystemExit(f"device-side status {raw.value:#x}: a bounded wait gave up; the timing is invalid")
 
     # ---- reduce over ranks: slowest rank's time, summed work
     flops_local = 2.0 * float(counts.sum()) * N * K
@@ -721,16 +882,17 @@ def main():
     elapsed_ms, e2e_ms = float(stats[0]), float(stats[1])
     flops_total, h2d_total, d2h_total = float(sums[0]), float(sums[1]), float(sums[2])
 
-    # one call launches one kernel per row-count bucket that the host-known row count can reach:
-    # <=32 rows (always), 33..128 rows, >=129 rows (CTA pairs)
-    launches_per_step = 1 + (int(counts.sum()) > 32) + (int(counts.sum()) >= 129)
+    # one call launches one kernel per row-count bucket that the host-known row count can reach: <=32 rows (always),
+    # 33..128 rows, >=129 rows (CTA pairs), plus a leading capped CTA-pair launch when the call is split
+    rows_local = int(counts.sum())
+    launches_per_step = 1 + (rows_local > 32) + (rows_local >= 129) + (rows_local >= 2048)
+    line = None
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
         value = flops_total / (ms_per_step * 1e-3) / 1e12
         peak, peak_kind = peak_hbm()
-        # roofline of the dominant (only) kernel, rank 0's launch: algorithmic bytes of rank 0's shard / its own time
+        # roofline of the call's kernel chain, rank 0's launch: algorithmic bytes of rank 0's shard / its own time
         abytes = algorithmic_bytes(counts, N, K)
-        my_ms = float(ev0.elapsed_time(ev1)) / args.steps
         achieved = abytes / (my_ms * 1e-3) / 1e9
         traffic = read_traffic(f"{args.workload}_n{world}")
         line = {
@@ -740,19 +902,43 @@ def main():
             "config": config,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": peak_kind, "algorithmic_bytes": abytes,
-                         "kernel": ("mxfp8_grouped_mm_kernel<32x10> + <128x6> + mxfp8_grouped_mm_pair_kernel "
-                                    "(one PDL chain per call)" if launches_per_step == 3 else "mxfp8_grouped_mm_kernel"),
+                         "kernel": ("mxfp8_grouped_mm_pair_kernel (capped) | mxfp8_grouped_mm_kernel<32x10> + <128x6> | "
+                                    "mxfp8_grouped_mm_pair_kernel: one PDL chain per call, buckets side by side"
+                                    if launches_per_step == 4 else "mxfp8_grouped_mm_kernel chain"),
                          "kernel_ms": my_ms},
-            "clocks": clocks, "gpu_launches": args.steps * launches_per_step,
+            "clocks": clocks, "gpu_launches": args.steps * launches_per_step, "host_us_per_call": host_us,
         }
+        if ref is not None:
+            line["impl"] = "reference"
+            line["reference_kind"] = ("gpu_kernel: the reference's own SM100 CUTLASS grouped GEMM, unmodified sources "
+                                      "built by oracle/build_ref.sh, called through its torch op")
+            line["roofline"]["kernel"] = "reference CUTLASS kernel (pre-compute + grouped GEMM)"
+            line["gpu_launches"] = args.steps * 2
         if e2e:
             e2e_step_ms = e2e_ms / args.steps
             line["e2e"] = {"value": flops_total / (e2e_step_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                            "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total),
                            "ms_per_step": e2e_step_ms}
+        if world == 1 and ref is None and not args.no_reference_gpu:
+            ref_side = reference_ops()
+            if ref_side is not None:
+                line["reference_gpu"] = compare_with_reference_kernel(
+                    wl, our_mm, ref_side.es_sm100_mxfp8_blockscaled_grouped_mm, device)
         if world == 1 and not args.no_cpu_baseline:
             r, cores, sdesc = cpu_reference_rate(counts_all, N, K, seed=100, budget_s=args.cpu_budget)
             line["cpu_baseline"] = {"value": r, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sdesc}
+    del wl
+    torch.cuda.empty_cache()
+    # N > 1, default workload: the expert-parallel layer (dispatch / combine over peer memory) rides along, outside the
+    # headline's timed region, so that a multi-GPU record also carries the exchange
+    if world > 1 and args.workload == "gate_up" and ref is None and args.ep_layer_steps > 0:
+        ep_args = argparse.Namespace(**vars(args))
+        ep_args.workload, ep_args.steps, ep_args.warmup = "qwen3_ep", args.ep_layer_steps, 3
+        ep_line = bench_ep_layer(ep_args, device, rank, world, dist)
+        if rank == 0:
+            line["ep_layer"] = {k: ep_line[k] for k in ("ms_per_step", "value", "unit", "device_status")}
+            line["ep_layer"]["workload"] = ep_line["config"]["workload"]
+    if rank == 0:
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()

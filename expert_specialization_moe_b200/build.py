@@ -26,7 +26,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
-] + (["-DES_PROFILE"] if os.environ.get("ES_PROFILE") else []) + os.environ.get("ES_NVCC_EXTRA", "").split()
+] + os.environ.get("ES_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:
@@ -82,6 +82,41 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+TORCH_SRC = PKG / "csrc_torch" / "es_b200_torch.cpp"
+TORCH_LIB = LIBDIR / "libes_b200_torch.so"
+TORCH_STAMP = LIBDIR / "libes_b200_torch.stamp"
+
+
+def build_torch_ops(force: bool = False) -> Path:
+    """The torch operator registration (TORCH_LIBRARY(es_b200)): one host-only C++ file compiled with g++ against the
+    installed torch headers and linked to libes_b200.so (found beside it through $ORIGIN)."""
+    import torch
+    build(force=False)
+    h = hashlib.sha256()
+    h.update(TORCH_SRC.read_bytes())
+    h.update((INCLUDE / "es_b200.h").read_bytes())
+    h.update(torch.__version__.encode())
+    fp = h.hexdigest()
+    if not force and TORCH_LIB.exists() and TORCH_STAMP.exists() and TORCH_STAMP.read_text().strip() == fp:
+        return TORCH_LIB
+    tdir = Path(torch.__file__).resolve().parent
+    cuda_home = Path(_nvcc()).resolve().parent.parent
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-std=c++17", "-O2", "-fPIC", "-shared",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
+           f"-I{tdir / 'include'}", f"-I{tdir / 'include' / 'torch' / 'csrc' / 'api' / 'include'}",
+           f"-I{cuda_home / 'include'}", f"-I{INCLUDE}", str(TORCH_SRC), "-o", str(TORCH_LIB),
+           f"-L{tdir / 'lib'}", "-ltorch", "-ltorch_cpu", "-lc10", "-lc10_cuda",
+           f"-L{LIBDIR}", "-les_b200", f"-L{cuda_home / 'lib64'}", "-lcudart",
+           "-Wl,-rpath,$ORIGIN", "-Wl,--no-undefined"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building the torch operator registration failed:\n{r.stdout}")
+    TORCH_STAMP.write_text(fp)
+    return TORCH_LIB
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    print(build_torch_ops(force="--force" in sys.argv))

@@ -1,4 +1,6 @@
 // Library-level entry points of the es_b200 C ABI: version, error strings, per-device property cache.
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -42,9 +44,42 @@ int get_device_info(DeviceInfo* out) {
   return ES_B200_OK;
 }
 
+static int env_or(const char* name, int fallback) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : fallback;
+}
+
+Tunables& tunables() {
+  static Tunables t = {
+      env_or("ES_B200_MM_HEAVY_MIN_ROWS", 0),      env_or("ES_B200_MM_TINY_MAX_ROWS", 0),
+      env_or("ES_B200_MM_PAIR_FIRST_CLUSTERS", 24), env_or("ES_B200_MM_SPLIT_MIN_ROWS", 2048),
+      env_or("ES_B200_MM_STREAM_MAX_CTAS", 0),     env_or("ES_B200_MM_PAIR_MAX_CLUSTERS", 0),
+      env_or("ES_B200_MM_DYNAMIC", 1),
+  };
+  return t;
+}
+
 }  // namespace es_b200
 
-extern "C" const char* es_b200_version(void) { return "es_b200 0.1 (sm_100a)"; }
+extern "C" int es_b200_set_tunable(const char* name, int value) {
+  using namespace es_b200;
+  ES_REQUIRE(name != nullptr, "null tunable name");
+  Tunables& t = tunables();
+  const struct { const char* n; int* p; } table[] = {
+      {"mm_heavy_min_rows", &t.mm_heavy_min_rows},         {"mm_tiny_max_rows", &t.mm_tiny_max_rows},
+      {"mm_pair_first_clusters", &t.mm_pair_first_clusters}, {"mm_split_min_rows", &t.mm_split_min_rows},
+      {"mm_stream_max_ctas", &t.mm_stream_max_ctas},       {"mm_pair_max_clusters", &t.mm_pair_max_clusters},
+      {"mm_dynamic", &t.mm_dynamic},
+  };
+  for (const auto& e : table)
+    if (strcmp(e.n, name) == 0) {
+      *e.p = value;
+      return ES_B200_OK;
+    }
+  return fail(ES_B200_ERR_INVALID_ARGUMENT, "unknown tunable '%s'", name);
+}
+
+extern "C" const char* es_b200_version(void) { return "es_b200 0.2 (sm_100a)"; }
 
 extern "C" const char* es_b200_last_error(void) { return es_b200::last_error_buffer(); }
 

@@ -1,0 +1,37 @@
+// Row-count thresholds of the MXFP8 grouped GEMM's tile-shape buckets per weight shape (n, k).
+//
+// The reference picks its bucket rules per device and by arithmetic intensity
+// (es_fp8_blockwise_functor.cuh:122-145,169-191,214-236: H20 and Hx00 use different filters).  Here the device is fixed
+// (B200) and what moves the best threshold is the weight shape: how long a tile streams one [128 x k] slab (k) and
+// how many CTAs one expert's tiles occupy (n).  Entries were measured with the sweep that lives beside the
+// benchmark's working files (each threshold pair timed on the shape with Zipf(1.2) row counts); shapes without an
+// entry use the default.
+#pragma once
+
+namespace es_b200 {
+
+struct BucketThresholds {
+  int tiny_max_rows;    // experts with at most this many rows: 128 x <=32 streaming tiles (at most 32)
+  int heavy_min_rows;   // experts with at least this many rows: CTA-pair tiles
+};
+
+struct BucketTableEntry {
+  int n, k;
+  BucketThresholds t;
+};
+
+constexpr BucketThresholds kDefaultBuckets = {32, 129};
+constexpr BucketTableEntry kBucketTable[] = {
+    {4096, 7168, {32, 129}},   // DeepSeek-V3 gate_up
+    {7168, 2048, {32, 129}},   // DeepSeek-V3 down
+    {1536, 2048, {32, 129}},   // Qwen3-30B-A3B gate_up
+    {2048, 768, {32, 129}},    // Qwen3-30B-A3B down
+};
+
+inline BucketThresholds bucket_thresholds(int n, int k) {
+  for (const BucketTableEntry& e : kBucketTable)
+    if (e.n == n && e.k == k) return e.t;
+  return kDefaultBuckets;
+}
+
+}  // namespace es_b200

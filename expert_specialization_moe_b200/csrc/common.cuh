@@ -6,6 +6,8 @@
 #include <cstdarg>
 #include <cstdio>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "es_b200.h"
 
 namespace es_b200 {
@@ -36,10 +38,100 @@ int get_device_info(DeviceInfo* out);   // for the current device
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- host: NVTX range around the launches of one operator call ---------------------------------
+// (header-only NVTX: a no-op unless a profiler is attached; makes a tool's launch list attributable per operator, as the
+// reference's benchmark does around its call: benchmark_sm100_mxfp8_blockscaled_moe.py:112-114)
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
+
+// ---- host: tunables of the tile-shape dispatcher -----------------------------------------------
+// One set per process; each has a built-in default, an environment override read once (ES_B200_<NAME in capitals>)
+// and can be changed at run time with es_b200_set_tunable.  A per-(n, k) table (bucket_table.cuh) supplies the
+// defaults of the two row-count thresholds; an explicit setting (environment or call) wins over the table.
+struct Tunables {
+  int mm_heavy_min_rows;        // MXFP8 GEMM: experts with at least this many rows go to the CTA-pair kernel; 0 = table
+  int mm_tiny_max_rows;         // experts with at most this many rows go to the 32-token streaming shape; 0 = table
+  int mm_pair_first_clusters;   // CTA pairs of the leading pair launch when a call is split (see grouped_mm_impl)
+  int mm_split_min_rows;        // calls with at least this many rows put a capped pair launch in front
+  int mm_stream_max_ctas;       // cap of the streaming kernels' grids (0 = one CTA per SM)
+  int mm_pair_max_clusters;     // cap of the trailing pair launch (0 = as many CTA pairs as fit)
+  int mm_dynamic;               // 1: tiles are dealt through the work counters in scratch when scratch is given
+};
+Tunables& tunables();
+
 // ---- device: programmatic dependent launch ---------------------------------------------------
 // Both are no-ops when the kernel was not launched with the programmatic-stream-serialization attribute.
 __device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---- device: work counters of the grouped GEMMs ------------------------------------------------
+// The scratch of a grouped GEMM call holds five 32-bit words, zero between calls:
+//   [0..2] next tile index of each of the three row-count buckets.  Every kernel of the call takes its tiles with
+//          atomicAdd on its bucket's word, so CTAs that start late (behind another kernel of the same call, on SMs
+//          that another bucket has just left) simply take what is left;
+//   [4]    CTAs of the call's earlier kernels that have finished (all their stores fenced);
+//   [3]    CTAs of the call's LAST kernel that have finished and seen [4] reach the number of earlier CTAs.
+// The kernels of a call are chained with programmatic dependent launch and only the first one waits for the stream's
+// earlier work; none of the others waits for its predecessor — a streaming kernel's CTAs leave their SMs to the next
+// kernel as soon as their bucket is empty, while a CTA-pair launch in front of them is still running.  What keeps
+// stream order for whatever follows the call is this rendezvous: every CTA of the last kernel, before it exits,
+// waits (bounded) until all earlier CTAs of the call have reported.  That wait cannot starve anybody: a dependent
+// launch only starts once every CTA of its predecessor is resident and has passed its launch_dependents, so by the
+// time a CTA of the last kernel runs, every CTA it waits for is already on an SM.  The last CTA to get through
+// clears the five words.
+constexpr int WORK_COUNTER_WORDS = 5;
+constexpr size_t GROUPED_MM_SCRATCH_BYTES = 256;
+constexpr uint32_t ERR_SCALE_OFFSET_BIT = 0x80u;   // a blockscale offset that is not a multiple of 128 rows
+constexpr uint32_t ERR_CALL_RENDEZVOUS_BIT = 0x200u;   // the last kernel gave up waiting for the call's earlier CTAs
+constexpr unsigned long long kRendezvousLimitNs = 4000000000ull;
+
+// Called by ALL threads of a CTA once its roles are done (in a CTA pair: by each CTA).  Without counters the kernels
+// keep stream order the simple way: every kernel but the first waits for its predecessor before it exits.
+__device__ __forceinline__ void end_of_kernel(uint32_t* counters, bool waited_at_start, bool last_of_call,
+                                              uint32_t earlier_ctas, bool peer_stores, uint32_t* status) {
+  if (counters == nullptr) {
+    if (!waited_at_start) pdl_wait_prior_grid();
+    return;
+  }
+  if (peer_stores) __threadfence_system(); else __threadfence();     // this thread's output stores
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  if (!last_of_call) {
+    atomicAdd(&counters[4], 1u);
+    return;
+  }
+  unsigned long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counters + 4) : "memory");
+    if (seen >= earlier_ctas) break;
+    if ((++spins & 63u) == 0) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kRendezvousLimitNs) {
+        atomicOr(status, ERR_CALL_RENDEZVOUS_BIT);
+        break;
+      }
+    }
+    __nanosleep(64);
+  }
+  __threadfence();
+  const uint32_t done = atomicAdd(&counters[3], 1u);
+  if (done == gridDim.x - 1) {
+    counters[0] = 0;
+    counters[1] = 0;
+    counters[2] = 0;
+    counters[4] = 0;
+    __threadfence();
+    counters[3] = 0;
+  }
+}
 
 // ---- device: block-wide exclusive scan of up to 1024 per-expert counts -----------------------
 // counts are produced by `f(e)` for e in [0, n); results go to prefix[0..n] (prefix[n] = total).

@@ -34,7 +34,7 @@ constexpr int THREADS = 256;                 // 8 warps, one row per warp
 constexpr int MAX_TOPK = 16;
 constexpr int MAX_WORLD = 16;
 constexpr uint32_t ERR_BAD_DESTINATION = 0x10000u, ERR_BARRIER_TIMEOUT = 0x20000u;
-constexpr unsigned long long BARRIER_LIMIT_NS = 5000000000ull;
+constexpr unsigned long long BARRIER_DEFAULT_LIMIT_NS = 5000000000ull;
 
 __device__ uint32_t g_status = 0;
 
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(THREADS)
 dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
                            const long long* __restrict__ dst_sf_offset, const __grid_constant__ PeerTable codes,
                            const __grid_constant__ PeerTable side, int my_rank, int world, int tokens, int topk, int k,
-                           long long capacity_rows) {
+                           long long capacity_rows, uint4* __restrict__ my_pairs, int pair_row_vec16) {
   // one side record per warp; dynamic, so that the kernel's footprint stays small enough to share an SM with a
   // grouped GEMM CTA of another stream
   extern __shared__ __align__(16) uint8_t side_s[];
@@ -80,6 +80,16 @@ dispatch_quant_push_kernel(const T* __restrict__ x, const int* __restrict__ dst_
       if (!(my_rank_j >= 0 && my_rank_j < world && my_row_j >= 0 && my_row_j < capacity_rows)) {
         atomicOr(&g_status, ERR_BAD_DESTINATION);
         my_rank_j = -1;
+      }
+    }
+    // A dropped pair sends nothing, so nothing comes back into its (token, j) slot: clear the slot here, or the
+    // weighted sum would add whatever an earlier step left there.  No peer writes this slot in this step, and stream
+    // order puts the store after the previous step's weighted sum.
+    if (my_pairs != nullptr) {
+      for (int d = 0; d < topk; ++d) {
+        if (__shfl_sync(0xffffffffu, my_rank_j, d) >= 0) continue;      // warp-uniform
+        uint4* slot = my_pairs + ((int64_t)t * topk + d) * pair_row_vec16;
+        for (int i = lane; i < pair_row_vec16; i += 32) slot[i] = make_uint4(0, 0, 0, 0);
       }
     }
     const T* in_row = x + (int64_t)t * k;
@@ -247,7 +257,8 @@ topk_weighted_sum_kernel(const uint4* __restrict__ pairs, const float* __restric
 
 // flags layout (uint32, in every GPU's symmetric buffer): [0, MAX_WORLD) epoch last announced by each GPU,
 // [MAX_WORLD] this GPU's own epoch counter (only ever touched by this GPU's barrier kernel).
-__global__ void __launch_bounds__(32) barrier_kernel(const __grid_constant__ PeerTable flags, int my_rank, int world) {
+__global__ void __launch_bounds__(32) barrier_kernel(const __grid_constant__ PeerTable flags, int my_rank, int world,
+                                                      unsigned long long limit_ns) {
   const int lane = threadIdx.x;
   uint32_t* mine = reinterpret_cast<uint32_t*>(flags.ptr[my_rank]);
   uint32_t epoch = 0;
@@ -267,7 +278,7 @@ __global__ void __launch_bounds__(32) barrier_kernel(const __grid_constant__ Pee
       if ((int32_t)(seen - epoch) >= 0) break;
       unsigned long long now;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-      if (now - t0 > BARRIER_LIMIT_NS) {
+      if (now - t0 > limit_ns) {
         atomicOr(&g_status, ERR_BARRIER_TIMEOUT);
         break;
       }
@@ -318,8 +329,10 @@ extern "C" int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const 
                                               const int32_t* dst_row, const int64_t* dst_scale_offset,
                                               const void* const* peer_codes, const void* const* peer_side, int my_rank,
                                               int world, int tokens, int topk, int k, int64_t capacity_rows,
-                                              void* stream) {
+                                              void* my_pairs, int pair_row_bytes, void* stream) {
   using namespace es_b200;
+  ES_REQUIRE(my_pairs == nullptr || (aligned16(my_pairs) && pair_row_bytes > 0 && pair_row_bytes % 16 == 0),
+             "my_pairs must be 16-byte aligned with rows of a multiple of 16 bytes");
   ES_REQUIRE(x_dtype == ES_B200_BF16 || x_dtype == ES_B200_FP16, "dtype must be kFloat16 or kBFloat16");
   ES_REQUIRE(k > 0 && k % 128 == 0 && k <= 16384, "k must align to 128 and be at most 16384");
   ES_REQUIRE(world >= 1 && world <= ep::MAX_WORLD, "world size must be in [1, %d]", ep::MAX_WORLD);
@@ -342,11 +355,11 @@ extern "C" int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const 
   if (x_dtype == ES_B200_BF16)
     ep::dispatch_quant_push_kernel<__nv_bfloat16><<<grid, ep::THREADS, side_smem, s>>>(
         static_cast<const __nv_bfloat16*>(x), dst_rank, dst_row, reinterpret_cast<const long long*>(dst_scale_offset),
-        codes, side, my_rank, world, tokens, topk, k, capacity_rows);
+        codes, side, my_rank, world, tokens, topk, k, capacity_rows, static_cast<uint4*>(my_pairs), pair_row_bytes / 16);
   else
     ep::dispatch_quant_push_kernel<__half><<<grid, ep::THREADS, side_smem, s>>>(
         static_cast<const __half*>(x), dst_rank, dst_row, reinterpret_cast<const long long*>(dst_scale_offset), codes,
-        side, my_rank, world, tokens, topk, k, capacity_rows);
+        side, my_rank, world, tokens, topk, k, capacity_rows, static_cast<uint4*>(my_pairs), pair_row_bytes / 16);
   ES_CUDA_TRY(cudaGetLastError());
   return ES_B200_OK;
 }
@@ -417,15 +430,22 @@ extern "C" int es_b200_ep_topk_weighted_sum(const void* pairs, int dtype, const 
   return ES_B200_OK;
 }
 
-extern "C" int es_b200_ep_barrier(const void* const* peer_flags, int my_rank, int world, void* stream) {
+extern "C" int es_b200_ep_barrier_limit(const void* const* peer_flags, int my_rank, int world, int64_t limit_ns,
+                                        void* stream) {
   using namespace es_b200;
+  ES_REQUIRE(limit_ns > 0, "the wait limit must be positive");
   ES_REQUIRE(world >= 1 && world <= ep::MAX_WORLD, "world size must be in [1, %d]", ep::MAX_WORLD);
   ES_REQUIRE(my_rank >= 0 && my_rank < world, "rank out of range");
   ES_REQUIRE(peer_flags, "null pointer argument");
   ep::PeerTable flags;
   int rc = ep::fill_table(&flags, peer_flags, world);
   if (rc != ES_B200_OK) return rc;
-  ep::barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, my_rank, world);
+  ep::barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, my_rank, world,
+                                                                      (unsigned long long)limit_ns);
   ES_CUDA_TRY(cudaGetLastError());
   return ES_B200_OK;
+}
+
+extern "C" int es_b200_ep_barrier(const void* const* peer_flags, int my_rank, int world, void* stream) {
+  return es_b200_ep_barrier_limit(peer_flags, my_rank, world, (int64_t)es_b200::ep::BARRIER_DEFAULT_LIMIT_NS, stream);
 }

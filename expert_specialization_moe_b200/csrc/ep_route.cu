@@ -11,6 +11,8 @@
 // a stable sort by expert followed by an all-to-all delivers.  A pair's rank among its GPU's pairs to the same expert
 // is found without sorting: the pairs are cut into 256 contiguous segments, one warp walks one segment 32 pairs at a
 // time (match_any gives the rank inside the step, a per-warp running count per expert the rank before it).
+#include <mutex>
+
 #include "common.cuh"
 #include "mxfp8_quant_math.cuh"
 
@@ -259,7 +261,9 @@ extern "C" int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, 
 // until the process exits, sized for at most ES_B200_ROUTE_STATIC_MAX_EXPERTS experts (256 KB).
 //
 // `g_route_static_counts` is a device symbol: in host code its name is only a handle.  Its device address is looked
-// up once per device (cudaGetSymbolAddress, with that device current) by the first call on that device and cached.
+// up once per device (cudaGetSymbolAddress, with that device current) by the first call on that device and cached
+// (under a lock); the cached address belongs to the device's primary context, so a process that destroys that context
+// (cudaDeviceReset) must not call the library again afterwards.
 // All calls on a device share the array: two calls that overlap on the GPU (different streams) would overwrite each
 // other's counters.  Nothing has to be cleared between calls — the count kernel writes every counter it later reads.
 static __device__ __align__(256) int32_t g_route_static_counts[es_b200::route::SEGMENTS * ES_B200_ROUTE_STATIC_MAX_EXPERTS];
@@ -273,14 +277,20 @@ extern "C" int es_b200_ep_route_count_static(const void* topk_ids, int ids_are_i
              "es_b200_ep_route_count with caller-provided scratch for more",
              ES_B200_ROUTE_STATIC_MAX_EXPERTS, num_experts);
   static int32_t* counters_of_device[64] = {nullptr};
+  static std::mutex mu;
   int dev = 0;
   ES_CUDA_TRY(cudaGetDevice(&dev));
   ES_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
-  if (counters_of_device[dev] == nullptr) {
-    int32_t* p = nullptr;
-    ES_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_static_counts));
-    counters_of_device[dev] = p;
+  int32_t* counters = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);       // first calls from several host threads
+    if (counters_of_device[dev] == nullptr) {
+      int32_t* p = nullptr;
+      ES_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_route_static_counts));
+      counters_of_device[dev] = p;
+    }
+    counters = counters_of_device[dev];
   }
-  return es_b200_ep_route_count(topk_ids, ids_are_int64, pairs, num_experts, counters_of_device[dev], segment_base,
-                                peer_counts_all, my_rank, world, stream);
+  return es_b200_ep_route_count(topk_ids, ids_are_int64, pairs, num_experts, counters, segment_base, peer_counts_all,
+                                my_rank, world, stream);
 }

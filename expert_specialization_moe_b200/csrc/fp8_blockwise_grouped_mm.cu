@@ -483,6 +483,7 @@ extern "C" int es_b200_fp8_blockwise_grouped_mm(const void* a, const void* b, co
                                                 const int32_t* problem_sizes, const int32_t* expert_offsets,
                                                 int num_experts, int64_t num_rows, int n, int k, void* scratch,
                                                 size_t scratch_bytes, void* stream) {
+  es_b200::NvtxRange nvtx_range("es_b200_fp8_blockwise_grouped_mm");
   using namespace es_b200;
   (void)scratch; (void)scratch_bytes;
   ES_REQUIRE(out_dtype == ES_B200_BF16 || out_dtype == ES_B200_FP16, "output must be bfloat16 or half");

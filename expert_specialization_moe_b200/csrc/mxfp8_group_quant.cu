@@ -189,6 +189,7 @@ extern "C" int es_b200_mxfp8_grouped_quant(const void* input, int input_dtype, c
                                            const int32_t* expert_offsets, const int32_t* blockscale_offsets,
                                            void* quant_output, uint8_t* scale_factor, int num_experts,
                                            int64_t num_rows, int k, void* stream) {
+  es_b200::NvtxRange nvtx_range("es_b200_mxfp8_grouped_quant");
   return es_b200::quant_impl<false>(input, input_dtype, problem_sizes, expert_offsets, blockscale_offsets, quant_output,
                                     scale_factor, num_experts, num_rows, k, stream);
 }
@@ -197,6 +198,7 @@ extern "C" int es_b200_mxfp8_silu_mul_grouped_quant(const void* gate_up, int inp
                                                     const int32_t* expert_offsets, const int32_t* blockscale_offsets,
                                                     void* quant_output, uint8_t* scale_factor, int num_experts,
                                                     int64_t num_rows, int k, void* stream) {
+  es_b200::NvtxRange nvtx_range("es_b200_mxfp8_silu_mul_grouped_quant");
   return es_b200::quant_impl<true>(gate_up, input_dtype, problem_sizes, expert_offsets, blockscale_offsets, quant_output,
                                    scale_factor, num_experts, num_rows, k, stream);
 }

@@ -6,7 +6,8 @@
 // of the expert sit on the MMA N axis.  N of tcgen05.mma can be any multiple of 16 up to 256, so a tile of an expert
 // with 3 tokens issues N=16 MMAs, one with 100 tokens N=112: the ragged dimension costs no padding to 128 and the
 // tail of an expert never needs a clipped tensor-map store.  Every tile streams a [128 x K] slab of the expert's
-// weights exactly once through a 6-stage TMA ring, which is what bounds the layer (weights dominate the bytes).
+// weights exactly once through a TMA ring (10 stages for tiles of at most 32 tokens, 6 stages for tiles of up to 128),
+// which is what bounds the layer (weights dominate the bytes).
 //
 //   warp 0    producer: TMA loads (weights tile, token tile, two 512-byte scale atoms) per 128-wide K step
 //   warp 1    tensor memory allocation + MMA issue (one elected lane): scale atoms smem -> TMEM (tcgen05.cp),
@@ -15,15 +16,19 @@
 //             each warp store writes 64 contiguous bytes of one output row; double-buffered against the MMAs
 //
 // Work list: tiles (expert, token tile of <=128, weight tile of 128) found with a per-CTA prefix scan over the
-// problem sizes (device resident: no host round trip), distributed round-robin over a persistent grid of one CTA
-// per SM.  Within an expert the token tile index runs fastest so that CTAs working at the same time read the same
-// weight slab (L2 reuse for heavy experts).
+// problem sizes (device resident: no host round trip).  The producer lane takes tile indices from the bucket's work
+// counter in the caller's scratch (atomicAdd; round-robin over the grid when the caller gave no scratch) and hands
+// each one to the MMA lane and the epilogue warps through a small shared-memory queue, so a CTA that starts late —
+// behind another kernel of the same call — just takes what is left.  Within an expert the token tile index runs
+// fastest so that CTAs working at the same time read the same weight slab (L2 reuse).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cstdlib>
 
+#include "bucket_table.cuh"
 #include "common.cuh"
 #include "epilogue.cuh"
+#include "grouped_mm_call.cuh"
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
@@ -57,12 +62,16 @@ constexpr uint32_t SFW_COL = 256;       // 4 columns: scales of the weight tile
 constexpr uint32_t SFX_COL = 260;       // 4 columns: scales of the token tile
 
 constexpr uint32_t ERR_PRODUCER = 1u, ERR_MMA = 2u, ERR_EPILOGUE = 4u;
+constexpr int QUEUE_DEPTH = 4;          // tile indices in flight between the producer lane and the other roles
 
 struct SharedCtl {
   uint64_t full[MAX_STAGES];
   uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t q_full[QUEUE_DEPTH];         // 1 arrival: the producer lane has written q_tile[slot]
+  uint64_t q_empty[QUEUE_DEPTH];        // 5 arrivals: the MMA lane and the four epilogue warps have read it
+  int q_tile[QUEUE_DEPTH];              // tile index, or -1: no more work
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
@@ -115,7 +124,8 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                         const uint8_t* __restrict__ sf_weights, OutT* __restrict__ d,
                         const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
                         const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
-                        int max_rows, int wait_at_start, const __grid_constant__ RowScatter scatter) {
+                        int max_rows, int wait_at_start, const __grid_constant__ RowScatter scatter,
+                        uint32_t* counters, int bucket, int last_of_call, uint32_t earlier_ctas) {
   constexpr int TOK_TILE = S::TOK_TILE, STAGES = S::STAGES, X_BYTES = S::X_BYTES, STAGE_BYTES = S::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -133,6 +143,10 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       ptx::mbar_init(&ctl->tmem_full[a], 1);
       ptx::mbar_init(&ctl->tmem_empty[a], 4);   // one arrival per epilogue warp
     }
+    for (int q = 0; q < QUEUE_DEPTH; ++q) {
+      ptx::mbar_init(&ctl->q_full[q], 1);
+      ptx::mbar_init(&ctl->q_empty[q], 5);
+    }
     ctl->abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&map_w);
@@ -148,13 +162,19 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   // Everything above is independent of the previous kernel's output; problem sizes may not be.  The first kernel
   // of a call waits here for whatever precedes the call; the later kernels of the same call are launched (programmatic
   // dependent launch) only after every CTA of the first has passed this point, so their operands are final: they
-  // start on SMs as they become free and wait for their predecessor only before they exit.
+  // start on SMs as they become free; stream order for what follows the call is kept at the end (end_of_kernel).
   if (wait_at_start) pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
   // this launch owns the experts with min_rows <= rows <= max_rows
+  // (an expert whose scales do not start on a 128-row atom cannot be addressed: reported and skipped)
   block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
-    return (m > 0 && m >= min_rows && m <= max_rows) ? ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles : 0;
+    if (!(m > 0 && m >= min_rows && m <= max_rows)) return 0;
+    if ((blockscale_offsets[e] & 127) != 0) {
+      atomicOr(&g_status, ERR_SCALE_OFFSET_BIT);
+      return 0;
+    }
+    return ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles;
   });
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -170,10 +190,25 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
+      int s = 0, qs = 0;
+      uint32_t ph = 0, qph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      uint32_t* counter = counters ? counters + bucket : nullptr;
+      int t = counter ? (int)atomicAdd(counter, 1u) : (int)blockIdx.x;
+      while (ok) {
+        // hand the tile index (or the end mark) to the other roles
+        if (!ptx::mbar_wait(&ctl->q_empty[qs], qph ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_PRODUCER);
+          break;
+        }
+        const bool live = t < total_tiles;
+        ctl->q_tile[qs] = live ? t : -1;
+        ptx::mbar_arrive(&ctl->q_full[qs]);
+        if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+        if (!live) break;
+        // the next index is requested now; its round trip to L2 hides behind this tile's loads
+        const int t_next = counter ? (int)atomicAdd(counter, 1u) : t + (int)gridDim.x;
         const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_x128;
         const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : 128u;
@@ -196,19 +231,29 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
           ptx::bulk_load(stage + W_BYTES + X_BYTES + SF_BYTES, sfx + (int64_t)kt * SF_BYTES, SF_BYTES, &ctl->full[s]);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
+        t = t_next;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
+      int s = 0, qs = 0;
+      uint32_t ph = 0, qph = 0;
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
       const uint32_t sfw_t = tmem_base + SFW_COL;
       const uint32_t sfx_t = tmem_base + SFX_COL;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      while (ok) {
+        if (!ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_MMA);
+          break;
+        }
+        const int t = ctl->q_tile[qs];
+        ptx::mbar_arrive(&ctl->q_empty[qs]);
+        if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+        if (t < 0) break;
         const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) { ok = false; }
         ptx::tc_fence_after_sync();
@@ -242,9 +287,22 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;   // TMEM lane quadrant this warp may access
-    int acc = 0;
-    uint32_t acc_ph = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    int acc = 0, qs = 0;
+    uint32_t acc_ph = 0, qph = 0;
+    while (true) {
+      const bool have = ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag);
+      if (!__all_sync(0xffffffffu, have)) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_EPILOGUE);
+        }
+        break;
+      }
+      const int t = ctl->q_tile[qs];
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&ctl->q_empty[qs]);
+      if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+      if (t < 0) break;
       const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
       const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
@@ -275,13 +333,13 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     __syncwarp();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
-  if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
+  end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
 }
 
+// earlier_ctas: in/out — CTAs launched so far by this call; the last kernel of the call waits for that many reports
 template <typename OutT, class S>
-int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
-           const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int min_rows,
-           int max_rows, bool first_of_call, const RowScatter& scatter, cudaStream_t stream) {
+int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bool last_of_call, int bucket,
+           uint32_t* earlier_ctas) {
   constexpr int TOK_TILE = S::TOK_TILE;
   constexpr size_t SMEM_BYTES = smem_bytes<S>();
   DeviceInfo info;
@@ -289,11 +347,11 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   if (rc != ES_B200_OK) return rc;
 
   CUtensorMap map_w, map_x[4];
-  rc = make_tensormap_u8_sw128(&map_w, b, (uint64_t)num_experts * n, (uint64_t)k, TILE_N);
+  rc = make_tensormap_u8_sw128(&map_w, c.b, (uint64_t)c.num_experts * c.n, (uint64_t)c.k, TILE_N);
   if (rc != ES_B200_OK) return rc;
   const uint32_t boxes[4] = {16, 32, 64, 128};
   for (int i = 0; i < 4; ++i) {
-    rc = make_tensormap_u8_sw128(&map_x[i], a, (uint64_t)num_rows, (uint64_t)k, boxes[i]);
+    rc = make_tensormap_u8_sw128(&map_x[i], c.a, (uint64_t)c.num_rows, (uint64_t)c.k, boxes[i]);
     if (rc != ES_B200_OK) return rc;
   }
 
@@ -306,34 +364,31 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
     configured[dev & 63] = true;
   }
   // upper bound of the tile count known on the host: full token tiles of num_rows plus one partial per expert
-  const int64_t max_tiles = ((num_rows + TOK_TILE - 1) / TOK_TILE + num_experts) * (int64_t)(n / TILE_N);
-  const int grid = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
+  const int64_t max_tiles = ((c.num_rows + TOK_TILE - 1) / TOK_TILE + c.num_experts) * (int64_t)(c.n / TILE_N);
+  int grid = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
+  const int cap = tunables().mm_stream_max_ctas;
+  if (cap > 0 && grid > cap) grid = cap;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = stream;
+  cfg.stream = c.stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sfa, sfb,
-                                 static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows, max_rows,
-                                 first_of_call ? 1 : 0, scatter));
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], c.sfa, c.sfb,
+                                 static_cast<OutT*>(c.d), c.ps, c.eo, c.bo, c.num_experts, c.n, c.k, min_rows, max_rows,
+                                 first_of_call ? 1 : 0, *c.scatter, c.counters, bucket, last_of_call ? 1 : 0,
+                                 *earlier_ctas));
+  *earlier_ctas += (uint32_t)grid;
   return ES_B200_OK;
 }
 
 }  // namespace mm
 
-namespace mm2 {   // CTA-pair kernel (mxfp8_grouped_mm_pair.cu)
-int launch_bf16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, int, int, const RowScatter&, cudaStream_t);
-int launch_fp16(const void*, const void*, const uint8_t*, const uint8_t*, void*, const int32_t*, const int32_t*,
-                const int32_t*, int, int64_t, int, int, int64_t, int, int, const RowScatter&, cudaStream_t);
-int read_and_clear_status(uint32_t* out);
-}  // namespace mm2
 namespace ep {    // expert-parallel dispatch / combine kernels (ep_dispatch_combine.cu)
 int read_and_clear_status(uint32_t* out);
 }
@@ -345,13 +400,16 @@ int read_and_clear_status(uint32_t* out);
 }
 }  // namespace es_b200
 
-extern "C" size_t es_b200_grouped_mm_scratch_bytes(int, int64_t, int, int) { return 0; }
+extern "C" size_t es_b200_grouped_mm_scratch_bytes(int, int64_t, int, int) {
+  return es_b200::GROUPED_MM_SCRATCH_BYTES;
+}
 
 namespace es_b200 {
 static int grouped_mm_impl(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, int out_dtype,
                            const int32_t* problem_sizes, const int32_t* expert_offsets,
                            const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n, int k,
-                           int64_t sfa_rows, const RowScatter& scatter, void* stream) {
+                           int64_t sfa_rows, const RowScatter& scatter, void* scratch, size_t scratch_bytes,
+                           void* stream) {
   ES_REQUIRE(out_dtype == ES_B200_BF16 || out_dtype == ES_B200_FP16, "dtype must be kFloat16 or kBFloat16");
   ES_REQUIRE(k > 0 && k % 128 == 0, "k should align 128");
   ES_REQUIRE(n > 0 && n % 128 == 0, "n should align 128");
@@ -364,53 +422,77 @@ static int grouped_mm_impl(const void* a, const void* b, const uint8_t* sfa, con
              "null pointer argument");
   ES_REQUIRE(aligned16(a) && aligned16(b) && aligned16(sfa) && aligned16(sfb), "a, b, sfa, sfb must be 16-byte aligned");
   ES_REQUIRE(aligned16(d), "d must be 16-byte aligned");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  ES_REQUIRE(sfa_rows >= 0, "sfa_rows must be non-negative");
+  if (scratch != nullptr) {
+    if (scratch_bytes < GROUPED_MM_SCRATCH_BYTES)
+      return fail(ES_B200_ERR_SCRATCH_TOO_SMALL, "scratch holds %zu bytes, es_b200_grouped_mm_scratch_bytes asks for %zu",
+                  scratch_bytes, GROUPED_MM_SCRATCH_BYTES);
+    ES_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "scratch must be 16-byte aligned");
+  }
   // Tile-shape specialisation.  Problem sizes live on the device, so the host cannot bucket the experts; instead
-  // both specialised kernels are always launched, back to back on the caller's stream with programmatic dependent
+  // one kernel per row-count bucket is launched, back to back on the caller's stream with programmatic dependent
   // launch, and each one filters the experts by row count inside its own work-list scan:
-  //   rows <= 32        : single-CTA kernel, 128 weights x <=32 tokens, 10-stage ring  \  these experts stream their
-  //   rows <= threshold : single-CTA kernel, 128 weights x <=128 tokens, 6-stage ring  /  weights from HBM exactly
-  //                       once; what counts is weight bytes in flight on every SM;
-  //   rows >  threshold : CTA-pair kernel, 256 weights x <=384 tokens, weight-stationary K step — these experts
+  //   rows <= tiny_max  : single-CTA kernel, 128 weights x <=32 tokens, 10-stage ring  \  these experts stream their
+  //   rows <  heavy_min : single-CTA kernel, 128 weights x <=128 tokens, 6-stage ring  /  weights from HBM exactly
+  //                       once; what counts is weight bytes in flight;
+  //   rows >= heavy_min : CTA-pair kernel, 256 weights x <=384 tokens, weight-stationary K step — these experts
   //                       re-read operands from L2, what counts is operand bytes per FLOP.
   // A kernel whose bucket is empty exits after its scan.  A bucket that even the host-known upper bound of rows per
-  // expert (num_rows) cannot reach is not launched at all.
-  // ES_B200_MM_HEAVY_MIN_ROWS overrides the threshold (1 = everything on CTA pairs, 0 = never).
-  static const int threshold = [] {
-    const char* v = getenv("ES_B200_MM_HEAVY_MIN_ROWS");
-    return v ? atoi(v) : 129;
-  }();
-  const int heavy_min = threshold <= 0 ? 0x7fffffff : threshold;
-  const int tiny_max = heavy_min - 1 < 32 ? heavy_min - 1 : 32;
+  // expert (num_rows) cannot reach is not launched at all.  The thresholds come from a per-(n, k) table
+  // (bucket_table.cuh) unless a tunable overrides them.
+  //
+  // With scratch (work counters) a large call is SPLIT: a pair launch capped to a few CTA pairs goes first, then the
+  // two streaming kernels on the SMs it leaves, then a second pair launch that takes the SMs the streaming kernels
+  // free and drains the same counter.  The streaming buckets are bound by HBM and leave the tensor pipe idle, the pair
+  // bucket is bound by the tensor pipe and leaves HBM idle: side by side the call costs about max() of the two
+  // instead of their sum.  Every kernel is persistent and takes tiles from its bucket's counter, and no kernel of the
+  // call waits for its predecessor (see end_of_kernel), so whichever side runs out first hands its SMs to the
+  // kernels queued behind it.
+  const Tunables& tn = tunables();
+  const BucketThresholds table = bucket_thresholds(n, k);
+  int heavy_min = tn.mm_heavy_min_rows > 0 ? tn.mm_heavy_min_rows : tn.mm_heavy_min_rows < 0 ? 0x7fffffff : table.heavy_min_rows;
+  int tiny_max = tn.mm_tiny_max_rows > 0 ? tn.mm_tiny_max_rows : table.tiny_max_rows;
+  if (tiny_max > 32) tiny_max = 32;
+  if (tiny_max > heavy_min - 1) tiny_max = heavy_min - 1;
   const bool bf16 = out_dtype == ES_B200_BF16;
+  mm::CallArgs c = {a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows, n, k,
+                    sfa_rows, &scatter, (tn.mm_dynamic && scratch) ? static_cast<uint32_t*>(scratch) : nullptr,
+                    static_cast<cudaStream_t>(stream)};
+
+  const bool want_tiny = tiny_max >= 1;
+  const bool want_mid = heavy_min - 1 > tiny_max && num_rows > tiny_max;
+  const bool want_pair = num_rows >= heavy_min;
+  const bool split = want_pair && c.counters != nullptr && (want_tiny || want_mid) &&
+                     num_rows >= tn.mm_split_min_rows && tn.mm_pair_first_clusters > 0;
   int rc = ES_B200_OK;
   bool first = true;
-  // <= 32 rows: 128 x <=32 tiles, 10-stage ring
-  if (tiny_max >= 1) {
-    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeTiny>(a, b, sfa, sfb, d, problem_sizes, expert_offsets,
-                                                         blockscale_offsets, num_experts, num_rows, n, k, 1, tiny_max,
-                                                         first, scatter, s)
-              : mm::launch<__half, mm::ShapeTiny>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets,
-                                                  num_experts, num_rows, n, k, 1, tiny_max, first, scatter, s);
+  uint32_t ctas = 0;       // CTAs launched so far by this call
+  auto pair = [&](int max_clusters, bool last) {
+    const int r = bf16 ? mm2::launch_bf16(c, heavy_min, max_clusters, first, last, &ctas)
+                       : mm2::launch_fp16(c, heavy_min, max_clusters, first, last, &ctas);
+    first = false;
+    return r;
+  };
+  if (split) {
+    rc = pair(tn.mm_pair_first_clusters, false);
+    if (rc != ES_B200_OK) return rc;
+  }
+  if (want_tiny) {
+    const bool last = !want_mid && !want_pair;
+    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeTiny>(c, 1, tiny_max, first, last, 0, &ctas)
+              : mm::launch<__half, mm::ShapeTiny>(c, 1, tiny_max, first, last, 0, &ctas);
     if (rc != ES_B200_OK) return rc;
     first = false;
   }
-  // 33 .. heavy_min-1 rows: 128 x <=128 tiles, 6-stage ring
-  if (heavy_min - 1 > tiny_max && num_rows > tiny_max) {
-    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeMid>(a, b, sfa, sfb, d, problem_sizes, expert_offsets,
-                                                        blockscale_offsets, num_experts, num_rows, n, k, tiny_max + 1,
-                                                        heavy_min - 1, first, scatter, s)
-              : mm::launch<__half, mm::ShapeMid>(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets,
-                                                 num_experts, num_rows, n, k, tiny_max + 1, heavy_min - 1, first, scatter, s);
+  if (want_mid) {
+    const bool last = !want_pair;
+    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeMid>(c, tiny_max + 1, heavy_min - 1, first, last, 1, &ctas)
+              : mm::launch<__half, mm::ShapeMid>(c, tiny_max + 1, heavy_min - 1, first, last, 1, &ctas);
     if (rc != ES_B200_OK) return rc;
     first = false;
   }
-  if (num_rows < heavy_min) return rc;
-  ES_REQUIRE(sfa_rows >= 0, "sfa_rows must be non-negative");
-  return bf16 ? mm2::launch_bf16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, scatter, s)
-              : mm2::launch_fp16(a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts,
-                                 num_rows, n, k, sfa_rows, heavy_min, first ? 1 : 0, scatter, s);
+  if (want_pair) rc = pair(tn.mm_pair_max_clusters, true);
+  return rc;
 }
 }  // namespace es_b200
 
@@ -418,10 +500,10 @@ extern "C" int es_b200_mxfp8_grouped_mm(const void* a, const void* b, const uint
                                         int out_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
                                         const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n,
                                         int k, int64_t sfa_rows, void* scratch, size_t scratch_bytes, void* stream) {
-  (void)scratch; (void)scratch_bytes;
+  es_b200::NvtxRange nvtx_range("es_b200_mxfp8_grouped_mm");
   es_b200::RowScatter dense = {};
   return es_b200::grouped_mm_impl(a, b, sfa, sfb, d, out_dtype, problem_sizes, expert_offsets, blockscale_offsets,
-                                  num_experts, num_rows, n, k, sfa_rows, dense, stream);
+                                  num_experts, num_rows, n, k, sfa_rows, dense, scratch, scratch_bytes, stream);
 }
 
 extern "C" int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
@@ -429,7 +511,9 @@ extern "C" int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, co
                                                 const int32_t* expert_offsets, const int32_t* blockscale_offsets,
                                                 int num_experts, int64_t num_rows, int n, int k, int64_t sfa_rows,
                                                 const int32_t* row_meta, const void* const* peer_out, int world,
-                                                int64_t slots_per_gpu, void* stream) {
+                                                int64_t slots_per_gpu, void* scratch, size_t scratch_bytes,
+                                                void* stream) {
+  es_b200::NvtxRange nvtx_range("es_b200_mxfp8_grouped_mm_scatter");
   using namespace es_b200;
   ES_REQUIRE(world >= 1 && world <= SCATTER_MAX_GPUS, "world size must be in [1, %d]", SCATTER_MAX_GPUS);
   ES_REQUIRE(row_meta && peer_out, "null pointer argument");
@@ -444,7 +528,7 @@ extern "C" int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, co
     sc.base[i] = const_cast<void*>(peer_out[i]);
   }
   return grouped_mm_impl(a, b, sfa, sfb, nullptr, out_dtype, problem_sizes, expert_offsets, blockscale_offsets,
-                         num_experts, num_rows, n, k, sfa_rows, sc, stream);
+                         num_experts, num_rows, n, k, sfa_rows, sc, scratch, scratch_bytes, stream);
 }
 
 extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {

@@ -22,6 +22,13 @@
 //   warp 18     leader CTA, one lane: sub-tile 1's four tcgen05.mma per K step
 //   warp 19     leader CTA, one lane: the K step's four tcgen05.cp (scales smem -> TMEM of both CTAs)
 //
+// Work items come from the bucket's work counter in the caller's scratch (atomicAdd by lane 0 of the leader's producer
+// warp; round-robin over the clusters without scratch).  The index travels to every other role of BOTH CTAs through a
+// four-deep queue: the leader writes it into its own and its partner's shared memory and arrives on both CTAs'
+// q_full barriers; every consuming role arrives on the leader's q_empty barrier.  Two launches of this kernel may
+// serve one call (a small one in front of the streaming kernels, a full-width one behind them): they drain the same
+// counter.
+//
 // Three issuing lanes instead of one because a tcgen05 instruction costs the thread that issues it ~90 cycles (mma)
 // or ~65 cycles (cp) whatever its size (measured: the K step of a single issuing lane took the same ~1000 cycles with
 // N = 64 and with N = 256 MMAs), while the tensor pipe needs 96 cycles for a 256 x 192 x 32 MMA.  One lane issuing
@@ -33,6 +40,7 @@
 
 #include "common.cuh"
 #include "epilogue.cuh"
+#include "grouped_mm_call.cuh"
 #include "sm100_ptx.cuh"
 #include "tensormap.cuh"
 
@@ -58,13 +66,16 @@ constexpr uint32_t SF_SLOT_COLS = 16;
 static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 
 constexpr uint32_t ERR_PRODUCER = 0x10u, ERR_MMA = 0x20u, ERR_EPILOGUE = 0x40u;
-constexpr uint32_t ERR_SCALE_OFFSET = 0x80u;   // a blockscale offset that is not a multiple of 128 rows
 constexpr uint32_t ERR_SCALE_COPY = 0x100u;
 constexpr int EPI_WARPS = 16;                              // per accumulator: 4 lane quadrants x 2 warps
 constexpr int EPI_TOK = 8;                                 // tokens per pass of an epilogue warp's shared-memory tile
 constexpr int EPI_BYTES_PER_WARP = EPI_TOK * 32 * 2;       // 512 bytes
 constexpr int MMA_B_WARP = 2 + EPI_WARPS;                  // 18
 constexpr int COPY_WARP = MMA_B_WARP + 1;                  // 19
+constexpr int QUEUE_DEPTH = 4;
+// readers of a queue slot: in the leader CTA the two MMA lanes, the copy lane and 16 epilogue warps; in the partner CTA
+// the producer warp and 16 epilogue warps
+constexpr int Q_CONSUMERS = (3 + EPI_WARPS) + (1 + EPI_WARPS);
 
 struct SharedCtl {
   uint64_t full[STAGES];        // used in the leader CTA only
@@ -73,28 +84,19 @@ struct SharedCtl {
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];       // used in the leader CTA only (16 arrivals: 8 epilogue warps x 2 CTAs)
                                 // index = accumulator (sub-tile 0 / 1)
+  uint64_t q_full[QUEUE_DEPTH];   // 1 arrival (from the leader's producer lane, in both CTAs): q_tile[slot] is written
+  uint64_t q_empty[QUEUE_DEPTH];  // leader only: Q_CONSUMERS arrivals, every consuming role of both CTAs has read it
+  int q_tile[QUEUE_DEPTH];        // work item index, or -1: no more work
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
   int tile_prefix[ES_B200_MAX_EXPERTS + 1];
-#ifdef ES_PROFILE
-  long long t_issue[STAGES];
-  long long t_commit[STAGES];
-#endif
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + EPI_WARPS * EPI_BYTES_PER_WARP + sizeof(SharedCtl);
 static_assert(SMEM_BYTES <= 232448, "shared memory of one CTA per SM");
 
 __device__ uint32_t g_status = 0;
-#ifdef ES_PROFILE
-__device__ unsigned long long g_prof[16];
-#define PROF_T0() long long _pt = clock64()
-#define PROF_ADD(i) do { long long _n = clock64(); _acc[i] += _n - _pt; _pt = _n; } while (0)
-#else
-#define PROF_T0()
-#define PROF_ADD(i)
-#endif
 
 struct TileInfo {
   int e, tt, np;
@@ -154,7 +156,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict__ d,
                              const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
                              const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
-                             int wait_at_start, const __grid_constant__ RowScatter scatter) {
+                             int wait_at_start, const __grid_constant__ RowScatter scatter, uint32_t* counters,
+                             int last_of_call, uint32_t earlier_ctas) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 16 x 512 bytes, one per epilogue warp
@@ -175,10 +178,11 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       ptx::mbar_init(&ctl->tmem_full[a], 1);
       ptx::mbar_init(&ctl->tmem_empty[a], EPI_WARPS);
     }
+    for (int q = 0; q < QUEUE_DEPTH; ++q) {
+      ptx::mbar_init(&ctl->q_full[q], 1);
+      ptx::mbar_init(&ctl->q_empty[q], Q_CONSUMERS);
+    }
     ctl->abort_flag = 0;
-#ifdef ES_PROFILE
-    for (int s = 0; s < STAGES; ++s) { ctl->t_issue[s] = 0; ctl->t_commit[s] = 0; }
-#endif
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&maps.w);
     ptx::prefetch_tensormap(&maps.sfw);
@@ -190,18 +194,24 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     ptx::tmem_alloc_pair(&ctl->tmem_base, TMEM_COLS);
     ptx::tmem_relinquish_pair();
   }
-  // Normally this kernel is launched behind the single-CTA kernels of the same call, with programmatic dependent
-  // launch.  The first kernel of the call waited for everything before it (griddepcontrol.wait) before it let the
-  // others start, so the operands are final; the kernels write disjoint rows of d.  This kernel therefore starts on
-  // SMs as they become free and only waits for its predecessor at the very end (below), which keeps stream order for
-  // whatever follows.  When it is the only kernel of the call it waits up front like any first kernel.
+  // This kernel is chained with the single-CTA kernels of the same call by programmatic dependent launch — behind
+  // them, and for a large call also in front of them with a capped grid.  The first kernel of the call waits for
+  // everything before it (griddepcontrol.wait) before it lets the others start, so the operands are final; the
+  // kernels write disjoint rows of d.  A launch that is not first therefore starts on SMs as they become free; stream
+  // order for whatever follows the call is kept at the end (end_of_kernel).
   if (wait_at_start) pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
   const int n_pairs = (n_tiles + 1) >> 1;
   // only experts with at least min_rows rows belong to this kernel (the single-CTA kernel takes the others)
+  // (an expert whose scales do not start on a 128-row atom cannot be addressed: reported and skipped)
   block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
-    return (m > 0 && m >= min_rows) ? ((m + TOK_TILE - 1) / TOK_TILE) * n_pairs : 0;
+    if (!(m > 0 && m >= min_rows)) return 0;
+    if ((blockscale_offsets[e] & 127) != 0) {
+      atomicOr(&g_status, ERR_SCALE_OFFSET_BIT);
+      return 0;
+    }
+    return ((m + TOK_TILE - 1) / TOK_TILE) * n_pairs;
   });
   // barriers and TMEM of both CTAs must exist before either CTA signals the other
   ptx::tc_fence_before_sync();
@@ -219,13 +229,47 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     // ------------------------------------------------------------------ producer (warp 0 of each CTA)
     // The whole warp walks the work list; per K step lanes 0..6 each issue ONE of the stage's loads in the same
     // instruction (a TMA issue costs the issuing thread ~80 cycles, five in a row would be a third of a stage time).
-    int s = 0;
-    uint32_t ph = 0;
-#ifdef ES_PROFILE
-    long long _acc[4] = {0, 0, 0, 0};
-#endif
-    PROF_T0();
-    for (int t = pair; t < total_tiles; t += num_pairs) {
+    int s = 0, qs = 0;
+    uint32_t ph = 0, qph = 0;
+    uint32_t* counter = counters ? counters + 2 : nullptr;
+    int t_mine = 0;                   // leader, lane 0: the index that goes out next
+    if (rank == 0 && lane == 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : pair;
+    while (true) {
+      // the leader publishes the next item (or the end mark) to both CTAs; the partner's producer reads its copy
+      int t = -1;
+      bool q_ok = true;
+      if (rank == 0) {
+        if (lane == 0) {
+          q_ok = ptx::mbar_wait(&ctl->q_empty[qs], qph ^ 1u, abort_flag);
+          if (q_ok) {
+            t = t_mine < total_tiles ? t_mine : -1;
+            ctl->q_tile[qs] = t;
+            ptx::st_shared_cluster_u32(&ctl->q_tile[qs], 1, (uint32_t)t);
+            ptx::mbar_arrive(&ctl->q_full[qs]);
+            ptx::mbar_arrive_cluster(&ctl->q_full[qs], 1);
+            // the following index is requested now; its round trip to L2 hides behind this item's loads
+            if (t >= 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : t_mine + num_pairs;
+          }
+        }
+        q_ok = __shfl_sync(0xffffffffu, (int)q_ok, 0) != 0;
+        t = __shfl_sync(0xffffffffu, t, 0);
+      } else {
+        q_ok = __all_sync(0xffffffffu, ptx::mbar_wait_cluster(&ctl->q_full[qs], qph, abort_flag));
+        if (q_ok) {
+          t = ctl->q_tile[qs];
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(&ctl->q_empty[qs], 0);
+        }
+      }
+      if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+      if (!q_ok) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_PRODUCER);
+        }
+        break;
+      }
+      if (t < 0) break;
       const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
       const int half0 = ti.n0 >> 1, half1 = ti.n1 >> 1;     // token rows of each sub-tile held by each CTA
       const int xi0 = box_index(half0), xi1 = box_index(half1);
@@ -235,8 +279,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       const int w_row = ti.e * n + nt * TILE_N;             // may run past the expert when n/128 is odd: not stored
       if (nt >= n_tiles) nt = n_tiles - 1;                  // keep the scale-atom load inside the buffer
       const int sfw_atom = ti.e * sfw_atoms_per_expert + nt * kt_count;
-      const int bs_off = blockscale_offsets[ti.e];
-      if ((bs_off & 127) != 0 && lane == 0) atomicOr(&g_status, ERR_SCALE_OFFSET);   // reported by es_b200_check_status
+      const int bs_off = blockscale_offsets[ti.e];          // a multiple of 128 (checked by the scan)
       const int sfx_atom = ((bs_off >> 7) + ti.atom0) * kt_count;
       // this lane's load: 0 weights, 1 tokens of sub-tile 0, 2 tokens of sub-tile 1, 3 weight scales,
       // 4..6 token scale atoms
@@ -255,10 +298,6 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       for (int kt = 0; kt < kt_count; ++kt) {
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag));
         if (!ok) break;
-        PROF_ADD(0);
-#ifdef ES_PROFILE
-        if (rank == 0 && lane == 0) { ctl->t_issue[s] = clock64(); if (ctl->t_commit[s]) _acc[2] += ctl->t_issue[s] - ctl->t_commit[s]; }
-#endif
         uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
         if (rank == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
         __syncwarp();
@@ -266,7 +305,6 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
           ptx::tma_load_2d_pair_hint(stage + my_off, my_map, &ctl->full[s], lane < 3 ? kt * TILE_K : 0,
                                      lane < 3 ? my_c1 : my_c1 + kt, my_hint);
         if (++s == STAGES) { s = 0; ph ^= 1u; }
-        PROF_ADD(1);
       }
       if (!ok) {
         if (lane == 0) {
@@ -276,42 +314,35 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         break;
       }
     }
-#ifdef ES_PROFILE
-    if (lane == 0) {
-      atomicAdd(&g_prof[0 + 4 * rank], (unsigned long long)_acc[0]);
-      atomicAdd(&g_prof[1 + 4 * rank], (unsigned long long)_acc[1]);
-      atomicAdd(&g_prof[2 + 4 * rank], (unsigned long long)_acc[2]);
-    }
-#endif
   } else if (warp == 1 || warp == MMA_B_WARP) {
     // ------------------------------------------------------------------ MMA issue (leader CTA): warp 1 issues the
-    // MMAs of sub-tile 0 into accumulator 0, warp 10 those of sub-tile 1 into accumulator 1
+    // MMAs of sub-tile 0 into accumulator 0, warp 18 those of sub-tile 1 into accumulator 1
     if (lane == 0 && rank == 0) {
       const int sub = warp == 1 ? 0 : 1;
-      int s = 0;
-      uint32_t ph = 0;
+      int s = 0, qs = 0;
+      uint32_t ph = 0, qph = 0;
       uint32_t acc_ph = 0;             // phase of this accumulator's empty barrier (advances once per use)
       bool ok = true;
-#ifdef ES_PROFILE
-      long long _acc[4] = {0, 0, 0, 0};
-      const long long _c0 = clock64();
-      const unsigned long long _g0 = ptx::globaltimer_ns();
-#endif
-      PROF_T0();
-      for (int t = pair; ok && t < total_tiles; t += num_pairs) {
+      while (ok) {
+        if (!ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_MMA);
+          break;
+        }
+        const int t = ctl->q_tile[qs];
+        ptx::mbar_arrive(&ctl->q_empty[qs]);
+        if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+        if (t < 0) break;
         const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         const uint32_t n_mma = sub == 0 ? ti.n0 : ti.n1;
         const uint32_t d_acc = tmem_base + sub * ACC_COLS;
         for (int kt = 0; ok && kt < kt_count; ++kt) {
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
-          PROF_ADD(1);
           if (n_mma > 0) {
             if (!ptx::mbar_wait(&ctl->sf_ready[s], ph, abort_flag)) { ok = false; break; }
-            PROF_ADD(3);
             if (kt == 0) {   // the previous item's epilogue must have drained this accumulator
               if (!ptx::mbar_wait(&ctl->tmem_empty[sub], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
               acc_ph ^= 1u;
-              PROF_ADD(0);
             }
             ptx::tc_fence_after_sync();
             const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -326,11 +357,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
                                     sfw_t | (j << 30), sfx_t | (j << 30), (kt | j) != 0 ? 1u : 0u);
           }
           ptx::tc_commit_pair(&ctl->empty[s], 3);       // this lane's share: both CTAs may refill once both have
-#ifdef ES_PROFILE
-          if (sub == 0) ctl->t_commit[s] = clock64();
-#endif
           if (++s == STAGES) { s = 0; ph ^= 1u; }
-          PROF_ADD(2);
         }
         if (!ok) {
           *abort_flag = 1;
@@ -339,24 +366,24 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         }
         if (n_mma > 0) ptx::tc_commit_pair(&ctl->tmem_full[sub], 3);     // this accumulator is complete in both CTAs
       }
-#ifdef ES_PROFILE
-      atomicAdd(&g_prof[sub == 0 ? 8 : 13], (unsigned long long)_acc[0]);
-      atomicAdd(&g_prof[sub == 0 ? 9 : 14], (unsigned long long)_acc[1]);
-      atomicAdd(&g_prof[sub == 0 ? 10 : 15], (unsigned long long)_acc[2]);
-      if (sub == 0) atomicAdd(&g_prof[11], 1ull);
-      if (sub == 0) atomicAdd(&g_prof[3], (unsigned long long)(clock64() - _c0));
-      if (sub == 0) atomicAdd(&g_prof[7], (unsigned long long)(ptx::globaltimer_ns() - _g0));
-      if (sub == 0) atomicAdd(&g_prof[12], (unsigned long long)_acc[3]);
-#endif
     }
   } else if (warp == COPY_WARP) {
     // ------------------------------------------------------------------ scale copies (leader CTA, one lane)
     // Token rows 0..383 of the item = scale atoms 0..2: sub-tile 0 reads atoms 0 and 1, sub-tile 1 atoms 1 and 2.
     if (lane == 0 && rank == 0) {
-      int s = 0;
-      uint32_t ph = 0;
+      int s = 0, qs = 0;
+      uint32_t ph = 0, qph = 0;
       bool ok = true;
-      for (int t = pair; ok && t < total_tiles; t += num_pairs) {
+      while (ok) {
+        if (!ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag)) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_SCALE_COPY);
+          break;
+        }
+        const int t = ctl->q_tile[qs];
+        ptx::mbar_arrive(&ctl->q_empty[qs]);
+        if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+        if (t < 0) break;
         const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
         for (int kt = 0; kt < kt_count; ++kt) {
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
@@ -383,8 +410,23 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     const int q = warp & 3;
     const int sub = (warp - 2) >> 3;
     const int half = ((warp - 2) >> 2) & 1;
-    uint32_t full_ph = 0;
-    for (int t = pair; t < total_tiles; t += num_pairs) {
+    uint32_t full_ph = 0, qph = 0;
+    int qs = 0;
+    while (true) {
+      const bool have = rank == 0 ? ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag)
+                                  : ptx::mbar_wait_cluster(&ctl->q_full[qs], qph, abort_flag);
+      if (!__all_sync(0xffffffffu, have)) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_EPILOGUE);
+        }
+        break;
+      }
+      const int t = ctl->q_tile[qs];
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(&ctl->q_empty[qs], 0);   // leader's barrier
+      if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+      if (t < 0) break;
       const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
       if (sub == 1 && ti.n1 == 0) continue;               // an item of <= 192 rows does not use accumulator 1
       const int nt = ti.np * 2 + (int)rank;
@@ -421,31 +463,30 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     __syncwarp();
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
-  if (!wait_at_start) pdl_wait_prior_grid();   // do not complete before the preceding kernel of this call has
+  end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
 }
 
 template <typename OutT>
-int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
-           const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k, int64_t sfa_rows,
-           int min_rows, int wait_at_start, const RowScatter& scatter, cudaStream_t stream) {
+int launch(const mm::CallArgs& c, int min_rows, int cluster_cap, bool first_of_call, bool last_of_call,
+           uint32_t* earlier_ctas) {
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
-  const int kt_count = k / TILE_K;
+  const int kt_count = c.k / TILE_K;
 
   Maps maps;
-  rc = make_tensormap_u8_sw128(&maps.w, b, (uint64_t)num_experts * n, (uint64_t)k, TILE_N);
+  rc = make_tensormap_u8_sw128(&maps.w, c.b, (uint64_t)c.num_experts * c.n, (uint64_t)c.k, TILE_N);
   if (rc != ES_B200_OK) return rc;
   const uint32_t boxes[5] = {8, 16, 32, 64, 96};
   for (int i = 0; i < 5; ++i) {
-    rc = make_tensormap_u8_sw128(&maps.x[i], a, (uint64_t)num_rows, (uint64_t)k, boxes[i]);
+    rc = make_tensormap_u8_sw128(&maps.x[i], c.a, (uint64_t)c.num_rows, (uint64_t)c.k, boxes[i]);
     if (rc != ES_B200_OK) return rc;
   }
-  rc = make_tensormap_records512(&maps.sfw, sfb, (uint64_t)num_experts * (n / TILE_N) * kt_count);
+  rc = make_tensormap_records512(&maps.sfw, c.sfb, (uint64_t)c.num_experts * (c.n / TILE_N) * kt_count);
   if (rc != ES_B200_OK) return rc;
   // whole 128-row atoms only; loads past the end read as zero (a map needs at least one record)
-  const uint64_t sfx_records = (uint64_t)(sfa_rows / 128) * kt_count;
-  rc = make_tensormap_records512(&maps.sfx, sfa, sfx_records ? sfx_records : 1);
+  const uint64_t sfx_records = (uint64_t)(c.sfa_rows / 128) * kt_count;
+  rc = make_tensormap_records512(&maps.sfx, c.sfa, sfx_records ? sfx_records : 1);
   if (rc != ES_B200_OK) return rc;
 
   auto kernel = mxfp8_grouped_mm_pair_kernel<OutT>;
@@ -459,7 +500,7 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = stream;
+  cfg.stream = c.stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
@@ -479,39 +520,28 @@ int launch(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb,
     if (nc < 1) return fail(ES_B200_ERR_CUDA, "no CTA pair of the grouped GEMM kernel fits on this device");
     resident_clusters[dev & 63] = nc;
   }
-  const int n_pairs = (n / TILE_N + 1) / 2;
-  const int64_t max_tiles = ((num_rows + TOK_TILE - 1) / TOK_TILE + num_experts) * (int64_t)n_pairs;
-  const int max_clusters = resident_clusters[dev & 63];
+  const int n_pairs = (c.n / TILE_N + 1) / 2;
+  const int64_t max_tiles = ((c.num_rows + TOK_TILE - 1) / TOK_TILE + c.num_experts) * (int64_t)n_pairs;
+  int max_clusters = resident_clusters[dev & 63];
+  if (cluster_cap > 0 && cluster_cap < max_clusters) max_clusters = cluster_cap;
   const int clusters = (int)(max_tiles < max_clusters ? max_tiles : max_clusters);
   cfg.gridDim = dim3(2 * clusters);
   cfg.numAttrs = 2;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(d), ps, eo, bo, num_experts, n, k, min_rows,
-                                 wait_at_start, scatter));
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, maps, static_cast<OutT*>(c.d), c.ps, c.eo, c.bo, c.num_experts, c.n, c.k,
+                                 min_rows, first_of_call ? 1 : 0, *c.scatter, c.counters, last_of_call ? 1 : 0,
+                                 *earlier_ctas));
+  *earlier_ctas += 2u * (uint32_t)clusters;
   return ES_B200_OK;
 }
 
-int launch_bf16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
-                const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, int min_rows, int wait_at_start, const RowScatter& scatter, cudaStream_t stream) {
-  return launch<__nv_bfloat16>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows,
-                               wait_at_start, scatter, stream);
+int launch_bf16(const mm::CallArgs& c, int min_rows, int max_clusters, bool first_of_call, bool last_of_call,
+                uint32_t* earlier_ctas) {
+  return launch<__nv_bfloat16>(c, min_rows, max_clusters, first_of_call, last_of_call, earlier_ctas);
 }
-int launch_fp16(const void* a, const void* b, const uint8_t* sfa, const uint8_t* sfb, void* d, const int32_t* ps,
-                const int32_t* eo, const int32_t* bo, int num_experts, int64_t num_rows, int n, int k,
-                int64_t sfa_rows, int min_rows, int wait_at_start, const RowScatter& scatter, cudaStream_t stream) {
-  return launch<__half>(a, b, sfa, sfb, d, ps, eo, bo, num_experts, num_rows, n, k, sfa_rows, min_rows, wait_at_start,
-                        scatter, stream);
+int launch_fp16(const mm::CallArgs& c, int min_rows, int max_clusters, bool first_of_call, bool last_of_call,
+                uint32_t* earlier_ctas) {
+  return launch<__half>(c, min_rows, max_clusters, first_of_call, last_of_call, earlier_ctas);
 }
-
-#ifdef ES_PROFILE
-extern "C" int es_b200_prof_read(unsigned long long* out16) {
-  unsigned long long z[16] = {0};
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out16, g_prof, sizeof(z));
-  cudaMemcpyToSymbol(g_prof, z, sizeof(z));
-  return 0;
-}
-#endif
 
 int read_and_clear_status(uint32_t* out) {
   uint32_t v = 0;

@@ -208,6 +208,44 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank
       ::"r"(smem_u32(bar)), "r"(rank)
       : "memory");
 }
+// store one 32-bit word at the same shared-memory offset in CTA `rank` of the cluster (distributed shared memory);
+// ordered before a following mbar_arrive_cluster by that arrive's release
+__device__ __forceinline__ void st_shared_cluster_u32(void* local_addr, uint32_t rank, uint32_t value) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 remAddr32;\n\t"
+      "mapa.shared::cluster.u32 remAddr32, %0, %1;\n\t"
+      "st.shared::cluster.u32 [remAddr32], %2;\n\t"
+      "}"
+      ::"r"(smem_u32(local_addr)), "r"(rank), "r"(value)
+      : "memory");
+}
+// bounded wait whose acquire covers writes made by the other CTA of the cluster before its arrive
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((++spins & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+  }
+}
 // In a cluster launch the shared-window address carries the CTA rank in bit 24; clearing it names the same offset in
 // the even CTA of the pair (the MMA leader).
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;

@@ -216,11 +216,13 @@ class ExpertShard:
             return work["out"]
         from . import _cabi
         meta, table, world, slots = scatter
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        scratch = _cabi.grouped_mm_scratch(dev, stream)
         _cabi.check(_cabi.load().es_b200_mxfp8_grouped_mm_scatter(
             work["a2"].data_ptr(), self.w2.data_ptr(), work["sfa2"].data_ptr(), self.sf2.data_ptr(), _cabi.BF16,
             ps2.data_ptr(), eo.data_ptr(), bo.data_ptr(), self.e_local, cap, self.h, self.i,
             work["sfa2"].numel() // (self.i // 32), meta.data_ptr(), table, world, slots,
-            torch.cuda.current_stream(dev).cuda_stream))
+            scratch.data_ptr(), scratch.numel(), stream))
         return None
 
     def forward(self, x: torch.Tensor, plan: DispatchPlan) -> torch.Tensor:
@@ -341,7 +343,7 @@ class FusedExchange:
         self._check(self._lib.es_b200_ep_dispatch_quant_push(
             x.data_ptr(), self._dtype_code, plan["dst_rank"].data_ptr(), plan["dst_row"].data_ptr(),
             plan["dst_scale_offset"].data_ptr(), self._peer_codes, self._peer_side, self.rank, self.world, self.tokens,
-            self.topk, self.hidden, self.capacity, s))
+            self.topk, self.hidden, self.capacity, self.pairs.data_ptr(), self.hidden * 2, s))
         self.barrier(x.device)                  # all ranks' stores into my buffers are complete and visible
         self._check(self._lib.es_b200_ep_unpack_side(self.side.data_ptr(), plan["total_rows"].data_ptr(),
                                                      self.scales.data_ptr(), self.meta.data_ptr(), self.hidden,

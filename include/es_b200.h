@@ -78,10 +78,16 @@ int es_b200_mxfp8_silu_mul_grouped_quant(const void* gate_up, int input_dtype, c
                                          int k, void* stream);
 
 /*
- * Scratch requirement (bytes, device memory, 256-byte aligned) of the two grouped GEMM entry points for a call
- * with these extents.  Stands where the reference allocates per-call torch::empty scratch tensors and a CUTLASS
- * workspace (es_sm100_mxfp8_blockscaled_launcher.cuh:163-176,140-142).  The kernels build their work lists in
- * shared memory, so this currently returns 0 and `scratch` may be NULL; callers should still ask.
+ * Scratch requirement (bytes of device memory, 16-byte aligned) of the MXFP8 grouped GEMM entry points.  Stands where
+ * the reference allocates per-call torch::empty scratch tensors and a CUTLASS workspace
+ * (es_sm100_mxfp8_blockscaled_launcher.cuh:163-176,140-142).  The kernels build their work lists in shared memory;
+ * the scratch only holds the work counters through which the kernels of one call share out their tiles.  Rules:
+ *   - zero it once (cudaMemset) before the first call that uses it; every call leaves it zeroed, so the same buffer
+ *     serves any number of calls on one stream, graph replays included;
+ *   - calls that may overlap on the GPU (different streams) need different scratch buffers;
+ *   - after es_b200_check_status has reported a device-side error, zero it again.
+ * scratch may be NULL: the kernels then deal their tiles round-robin and a large call runs its row-count buckets one
+ * after the other instead of side by side (slower, same results).
  */
 size_t es_b200_grouped_mm_scratch_bytes(int num_experts, int64_t num_rows, int n, int k);
 
@@ -131,7 +137,8 @@ int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, const uint8_t
                                      int out_dtype, const int32_t* problem_sizes, const int32_t* expert_offsets,
                                      const int32_t* blockscale_offsets, int num_experts, int64_t num_rows, int n,
                                      int k, int64_t sfa_rows, const int32_t* row_meta, const void* const* peer_out,
-                                     int world, int64_t slots_per_gpu, void* stream);
+                                     int world, int64_t slots_per_gpu, void* scratch, size_t scratch_bytes,
+                                     void* stream);
 
 /*
  * Expert-parallel exchange over peer memory (one process per GPU; the experts of a layer are spread over the GPUs of a
@@ -149,7 +156,10 @@ int es_b200_mxfp8_grouped_mm_scatter(const void* a, const void* b, const uint8_t
  *   of peer_side[dst_rank[pair]] ([capacity_rows, es_b200_ep_side_record_bytes(k)] bytes): { int32 my_rank, int32
  *   pair, int64 dst_scale_offset[pair], k/32 scale bytes }.  dst_scale_offset = byte offset of the row's scale word
  *   for K tile 0 in the owner's swizzled scale buffer (blockscale_offset * k/32 + the row's position inside its
- *   expert).
+ *   expert).  A pair whose destination is out of range (an expert id outside [0, E), or a row past the owner's
+ *   capacity) is dropped and reported; if my_pairs is given (this GPU's [tokens * topk, pair_row_bytes] slot buffer
+ *   that the expert outputs come back to, or NULL), the dropped pair's slot is cleared so that the weighted sum adds 0
+ *   for it instead of a row left by an earlier step.
  * es_b200_ep_unpack_side (local, after the barrier): for rows r < *num_rows_dev of `side`, writes the scale bytes to
  *   `scales` (swizzled layout, scale_bytes long) and (source GPU, pair) to meta[r] ([capacity_rows, 2] int32).
  * es_b200_ep_combine_push: stores row r < *num_rows_dev of y [capacity_rows, n] (2-byte elements) to row meta[r][1]
@@ -164,7 +174,7 @@ int es_b200_ep_side_record_bytes(int k);
 int es_b200_ep_dispatch_quant_push(const void* x, int x_dtype, const int32_t* dst_rank, const int32_t* dst_row,
                                    const int64_t* dst_scale_offset, const void* const* peer_codes,
                                    const void* const* peer_side, int my_rank, int world, int tokens, int topk, int k,
-                                   int64_t capacity_rows, void* stream);
+                                   int64_t capacity_rows, void* my_pairs, int pair_row_bytes, void* stream);
 int es_b200_ep_unpack_side(const void* side, const int32_t* num_rows_dev, uint8_t* scales, int32_t* meta, int k,
                            int64_t capacity_rows, int64_t scale_bytes, void* stream);
 int es_b200_ep_combine_push(const void* y, const int32_t* meta, const int32_t* num_rows_dev,
@@ -173,6 +183,8 @@ int es_b200_ep_combine_push(const void* y, const int32_t* meta, const int32_t* n
 int es_b200_ep_topk_weighted_sum(const void* pairs, int dtype, const float* weights, void* out, int tokens, int topk,
                                  int n, void* stream);
 int es_b200_ep_barrier(const void* const* peer_flags, int my_rank, int world, void* stream);
+/* the same with the wait limit given by the caller (nanoseconds) instead of five seconds */
+int es_b200_ep_barrier_limit(const void* const* peer_flags, int my_rank, int world, int64_t limit_ns, void* stream);
 
 /*
  * Routing tables of the exchange, on the device (no counterpart in the reference).  topk_ids holds this GPU's
@@ -205,7 +217,8 @@ int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, int pairs, 
  * device array inside the library (256 KB per GPU, held until the process exits) instead of `segment_counts`.
  * Limits and rules: num_experts <= ES_B200_ROUTE_STATIC_MAX_EXPERTS, otherwise ES_B200_ERR_INVALID_ARGUMENT and
  * nothing is launched; the call allocates and frees nothing; the first call on each device looks up the array's device
- * address (make that first call outside any stream capture); all calls on one device share the array, so calls that
+ * address (make that first call outside any stream capture; the address is cached for the life of the device's primary
+ * context, so do not call the library after a cudaDeviceReset); all calls on one device share the array, so calls that
  * overlap on the GPU (different streams) race — serialise them.  Inputs, outputs and results are those of
  * es_b200_ep_route_count.
  */
@@ -213,6 +226,16 @@ int es_b200_ep_route_tables(const void* topk_ids, int ids_are_int64, int pairs, 
 int es_b200_ep_route_count_static(const void* topk_ids, int ids_are_int64, int pairs, int num_experts,
                                   int32_t* segment_base, const void* const* peer_counts_all, int my_rank, int world,
                                   void* stream);
+
+/*
+ * Tunables of the tile-shape dispatcher (no counterpart in the reference, whose bucket rules are compile-time
+ * functors: es_fp8_blockwise_functor.cuh:122-256).  Process-wide; each also has an environment override read once,
+ * ES_B200_<NAME IN CAPITALS>.  Names: "mm_heavy_min_rows" (experts with at least this many rows use CTA-pair tiles;
+ * 0 = per-(n, k) table, negative = never), "mm_tiny_max_rows" (0 = table), "mm_pair_first_clusters",
+ * "mm_split_min_rows", "mm_stream_max_ctas", "mm_pair_max_clusters" (grid shaping of a split call, 0 = no cap),
+ * "mm_dynamic" (0: ignore the work counters).  Unknown name: ES_B200_ERR_INVALID_ARGUMENT.
+ */
+int es_b200_set_tunable(const char* name, int value);
 
 /*
  * Device-side status word of the grouped GEMMs.  Every wait inside the kernels is bounded; a wait that gives up

@@ -1,16 +1,21 @@
 """TEST INFRASTRUCTURE ONLY.  Single-GPU A/B of this library's kernels against the reference's own SM100 kernels
-(oracle/_ref/libes_reference.so, built by oracle/build_ref.sh) on identical device inputs.
+(oracle/_ref/libes_reference.so, built by oracle/build_ref.sh) on identical device inputs, in one process.
 
-    python oracle/compare_with_reference_gpu.py [--workload gate_up|down] [--steps 20] [--quant]
+    python oracle/compare_with_reference_gpu.py [--workloads gate_up,down,heavy,ref_dist,ref_dist_ep8] [--steps 20,200]
+                                                [--repeats 5] [--quant]
 
-Prints one JSON line per measurement: device time per call (CUDA events, after warm-up) of both implementations and
-the output agreement.  Never run on more than one GPU: the reference kernel issues cluster-multicast TMA loads.
+For every workload and step count the two implementations run INTERLEAVED (ours, reference, ours, reference, ...),
+`repeats` timed groups of `steps` calls each (CUDA events on the launching stream, after warm-up); the SM clock is
+sampled with nvidia-smi while each arm runs (groups of 100 calls or more).  One JSON line per measurement: medians of ms per call for both arms,
+their ratio, ms x median SM MHz (what the call costs in SM cycles, comparable across power-cap states) and the output
+agreement.  Never run on more than one GPU: the reference kernel issues cluster-multicast TMA loads.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import sys
+import time
 from pathlib import Path
 
 import numpy as np
@@ -21,46 +26,79 @@ sys.path.insert(0, str(ROOT))
 import bench  # noqa: E402
 
 
-def timeit(fn, steps, warmup=5):
-    for _ in range(warmup):
+def timed_group(fn, steps, dev):
+    # the clock is only sampled on long groups: nvidia-smi needs a few hundred ms to start delivering samples
+    sample = steps >= 100
+    sampler = bench.ClockSampler(dev.index or 0)
+    if sample:
+        sampler.start()
+        time.sleep(0.3)
         fn()
-    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
         fn()
     e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / steps
+    torch.cuda.synchronize(dev)
+    clocks = sampler.stop() if sample else {}
+    return e0.elapsed_time(e1) / steps, clocks.get("sm_mhz")
+
+
+def interleaved(ours, ref, steps, repeats, dev):
+    for _ in range(3):
+        ours(); ref()
+    torch.cuda.synchronize(dev)
+    t_o, t_r, c_o, c_r = [], [], [], []
+    for _ in range(repeats):
+        t, c = timed_group(ours, steps, dev); t_o.append(t); c_o.append(c)
+        t, c = timed_group(ref, steps, dev); t_r.append(t); c_r.append(c)
+    med = lambda v: float(np.median([x for x in v if x is not None])) if any(x is not None for x in v) else None
+    mo, mr, co, cr = med(t_o), med(t_r), med(c_o), med(c_r)
+    out = {"steps": steps, "repeats": repeats, "ours_ms": mo, "reference_ms": mr, "speedup": mr / mo,
+           "ours_ms_all": [round(x, 4) for x in t_o], "reference_ms_all": [round(x, 4) for x in t_r],
+           "ours_sm_mhz": co, "reference_sm_mhz": cr}
+    if co and cr:
+        out["ours_ms_x_mhz"], out["reference_ms_x_mhz"] = mo * co, mr * cr
+        out["speedup_in_sm_cycles"] = (mr * cr) / (mo * co)
+    return out
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="gate_up")
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--workloads", default="gate_up,down,heavy,ref_dist,ref_dist_ep8")
+    ap.add_argument("--steps", default="20,200")
+    ap.add_argument("--repeats", type=int, default=5)
     ap.add_argument("--quant", action="store_true", help="also compare the grouped quant at T=32768,K=7168,E=256")
     args = ap.parse_args()
-    torch.ops.load_library(str(ROOT / "oracle" / "_ref" / "libes_reference.so"))
-    ref = torch.ops.expert_specialization
+    assert torch.cuda.device_count() >= 1
+    ref = bench.reference_ops()
+    assert ref is not None, "oracle/_ref/libes_reference.so is missing: run oracle/build_ref.sh"
     from expert_specialization_moe_b200 import (es_sm100_mxfp8_blockscaled_grouped_mm as our_mm,
                                                 es_sm100_mxfp8_blockscaled_grouped_quant as our_quant)
     dev = torch.device("cuda", 0)
-    E, T, N, K, desc = bench.WORKLOADS[args.workload]
-    counts = bench.zipf_counts(T, E, 1.2, 0)
-    wl = bench.build_device_workload(counts, N, K, dev, seed=1000)
-    flops = 2.0 * T * N * K
-    abytes = bench.algorithmic_bytes(counts, N, K)
+    torch.cuda.set_device(dev)
+    step_counts = [int(x) for x in args.steps.split(",")]
 
-    d_ref = torch.zeros_like(wl["d"])
-    t_ours = timeit(lambda: our_mm(wl["d"], wl["a"], wl["b"], wl["sfa"], wl["sfb"], wl["ps"], wl["eo"], wl["bo"]), args.steps)
-    t_ref = timeit(lambda: ref.es_sm100_mxfp8_blockscaled_grouped_mm(wl["a"], wl["b"], wl["sfa"], wl["sfb"], d_ref, wl["ps"], wl["eo"], wl["bo"]), args.steps)
-    x, y = wl["d"].float(), d_ref.float()
-    rel = float((x - y).norm() / y.norm())
-    same = float((wl["d"].view(torch.int16) == d_ref.view(torch.int16)).float().mean())
-    print(json.dumps({"op": "mxfp8_grouped_mm", "workload": desc, "ours_ms": t_ours, "reference_ms": t_ref,
-                      "speedup": t_ref / t_ours, "ours_tflops": flops / t_ours / 1e9, "reference_tflops": flops / t_ref / 1e9,
-                      "ours_gbs": abytes / t_ours / 1e6, "reference_gbs": abytes / t_ref / 1e6,
-                      "rel_diff_vs_reference": rel, "bit_identical_fraction": same}))
+    for name in [w for w in args.workloads.split(",") if w]:
+        E, T, N, K, desc = bench.WORKLOADS[name]
+        counts = bench.workload_counts(name)
+        T = int(counts.sum())
+        wl = bench.build_device_workload(counts, N, K, dev, seed=1000)
+        d_ref = torch.zeros_like(wl["d"])
+        ours = lambda: our_mm(wl["d"], wl["a"], wl["b"], wl["sfa"], wl["sfb"], wl["ps"], wl["eo"], wl["bo"])
+        theirs = lambda: ref.es_sm100_mxfp8_blockscaled_grouped_mm(wl["a"], wl["b"], wl["sfa"], wl["sfb"], d_ref,
+                                                                   wl["ps"], wl["eo"], wl["bo"])
+        flops = 2.0 * T * N * K
+        abytes = bench.algorithmic_bytes(counts, N, K)
+        for steps in step_counts:
+            r = interleaved(ours, theirs, steps, args.repeats, dev)
+            same = float((wl["d"].view(torch.int16) == d_ref.view(torch.int16)).float().mean())
+            r.update({"op": "mxfp8_grouped_mm", "workload": name, "ours_tflops": flops / r["ours_ms"] / 1e9,
+                      "reference_tflops": flops / r["reference_ms"] / 1e9, "ours_gbs": abytes / r["ours_ms"] / 1e6,
+                      "reference_gbs": abytes / r["reference_ms"] / 1e6, "bit_identical_fraction": same})
+            print(json.dumps(r), flush=True)
+        del wl, d_ref
+        torch.cuda.empty_cache()
 
     if args.quant:
         Tq, Kq, Eq = 32768, 7168, 256
@@ -74,12 +112,15 @@ def main():
         c2 = torch.zeros_like(c1)
         s1 = torch.zeros((sf_rows, Kq // 32), dtype=torch.uint8, device=dev)
         s2 = torch.zeros_like(s1)
-        tq_ours = timeit(lambda: our_quant(xq, ps, eo, bo, c1, s1), args.steps)
-        tq_ref = timeit(lambda: ref.es_sm100_mxfp8_blockscaled_grouped_quant(xq, ps, eo, bo, c2, s2), args.steps)
         qbytes = 2 * Tq * Kq + Tq * Kq + Tq * Kq // 32
-        print(json.dumps({"op": "mxfp8_grouped_quant", "T": Tq, "K": Kq, "E": Eq, "ours_ms": tq_ours, "reference_ms": tq_ref,
-                          "speedup": tq_ref / tq_ours, "ours_gbs": qbytes / tq_ours / 1e6, "reference_gbs": qbytes / tq_ref / 1e6,
-                          "codes_identical": bool(torch.equal(c1.view(torch.uint8), c2.view(torch.uint8)))}))
+        for steps in step_counts:
+            r = interleaved(lambda: our_quant(xq, ps, eo, bo, c1, s1),
+                            lambda: ref.es_sm100_mxfp8_blockscaled_grouped_quant(xq, ps, eo, bo, c2, s2), steps,
+                            args.repeats, dev)
+            r.update({"op": "mxfp8_grouped_quant", "workload": "quant", "ours_gbs": qbytes / r["ours_ms"] / 1e6,
+                      "reference_gbs": qbytes / r["reference_ms"] / 1e6,
+                      "codes_identical": bool(torch.equal(c1.view(torch.uint8), c2.view(torch.uint8)))})
+            print(json.dumps(r), flush=True)
 
 
 if __name__ == "__main__":

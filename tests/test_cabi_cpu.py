@@ -41,7 +41,8 @@ def test_argument_checks_happen_before_any_launch(lib):
     assert rc == 1 and b"Number of experts cannot exceed 1024" in lib.es_b200_last_error()
     rc = lib.es_b200_fp8_blockwise_grouped_mm(None, None, None, None, None, 0, None, None, 4, 16, 100, 128, None, 0, None)
     assert rc == 1 and b"n should align 128" in lib.es_b200_last_error()
-    assert lib.es_b200_grouped_mm_scratch_bytes(8, 512, 1024, 512) == 0
+    assert lib.es_b200_grouped_mm_scratch_bytes(8, 512, 1024, 512) == 256      # the work counters
+    assert lib.es_b200_set_tunable(b"no_such_tunable", 1) == 1 and b"unknown tunable" in lib.es_b200_last_error()
 
 
 def test_ops_mirror_reference_signatures():
@@ -58,12 +59,37 @@ def test_ops_mirror_reference_signatures():
 
 
 def test_ops_have_no_cpu_fallback():
+    """As in the reference, only a CUDA kernel is registered: the dispatcher refuses CPU tensors."""
     from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_quant as quant
     x = torch.zeros((4, 128), dtype=torch.bfloat16)
     ps = torch.tensor([[4, 0, 128]], dtype=torch.int32)
     z = torch.zeros(1, dtype=torch.int32)
-    with pytest.raises(RuntimeError, match="CUDA-only"):
+    with pytest.raises(RuntimeError, match="CPU"):
         quant(x, ps, z, z, torch.zeros((4, 128), dtype=torch.uint8), torch.zeros((128, 4), dtype=torch.uint8))
+
+
+# the operator schemas of the reference extension (expert_specialization/csrc/expert_specialization.cpp:57-66)
+REFERENCE_SCHEMAS = {
+    "es_fp8_blockwise_scaled_grouped_mm":
+        "(Tensor output, Tensor a, Tensor b, Tensor scales_a, Tensor scales_b, Tensor stride_a, Tensor stride_b, "
+        "Tensor stride_d, Tensor problem_sizes, Tensor expert_offsets, Tensor workspace) -> ()",
+    "es_sm100_mxfp8_blockscaled_grouped_mm":
+        "(Tensor a, Tensor b, Tensor sfa, Tensor sfb, Tensor d, Tensor problem_sizes, Tensor expert_offsets, "
+        "Tensor blockscale_offsets) -> ()",
+    "es_sm100_mxfp8_blockscaled_grouped_quant":
+        "(Tensor input, Tensor problem_sizes, Tensor expert_offsets, Tensor blockscale_offsets, Tensor quant_output, "
+        "Tensor scale_factor) -> ()",
+}
+
+
+def test_torch_ops_are_registered_with_the_reference_schemas():
+    from expert_specialization_moe_b200 import _cabi
+    ops = _cabi.torch_ops()
+    for name, want in REFERENCE_SCHEMAS.items():
+        schema = str(getattr(ops, name).default._schema)
+        assert schema == f"es_b200::{name}{want}", schema
+        keys = torch._C._dispatch_dump(f"es_b200::{name}")
+        assert "CUDA" in keys and "CPU:" not in keys, keys          # CUDA dispatch key only, as in the reference
 
 
 def test_product_does_not_import_the_oracle():
