@@ -12,7 +12,8 @@ namespace es_b200 {
 
 struct BucketThresholds {
   int tiny_max_rows;    // experts with at most this many rows: 128 x <=32 streaming tiles (at most 32)
-  int heavy_min_rows;   // experts with at least this many rows: CTA-pair tiles
+  int heavy_min_rows;   // experts with at least this many rows: CTA-pair tiles (at most 113: the larger streaming
+                        // shape holds 112 token rows)
 };
 
 struct BucketTableEntry {
@@ -20,12 +21,12 @@ struct BucketTableEntry {
   BucketThresholds t;
 };
 
-constexpr BucketThresholds kDefaultBuckets = {32, 129};
+constexpr BucketThresholds kDefaultBuckets = {32, 113};
 constexpr BucketTableEntry kBucketTable[] = {
-    {4096, 7168, {32, 129}},   // DeepSeek-V3 gate_up
-    {7168, 2048, {32, 129}},   // DeepSeek-V3 down
-    {1536, 2048, {32, 129}},   // Qwen3-30B-A3B gate_up
-    {2048, 768, {32, 129}},    // Qwen3-30B-A3B down
+    {4096, 7168, {32, 113}},   // DeepSeek-V3 gate_up
+    {7168, 2048, {32, 113}},   // DeepSeek-V3 down
+    {1536, 2048, {32, 113}},   // Qwen3-30B-A3B gate_up
+    {2048, 768, {32, 113}},    // Qwen3-30B-A3B down
 };
 
 inline BucketThresholds bucket_thresholds(int n, int k) {

@@ -60,6 +60,7 @@ struct Tunables {
   int mm_stream_max_ctas;       // cap of the streaming kernels' grids (0 = one CTA per SM)
   int mm_pair_max_clusters;     // cap of the trailing pair launch (0 = as many CTA pairs as fit)
   int mm_dynamic;               // 1: tiles are dealt through the work counters in scratch when scratch is given
+  int mm_stream_lsu;            // 1: the streaming kernels fill every other ring slot with cp.async instead of TMA
 };
 Tunables& tunables();
 

@@ -114,6 +114,48 @@ __device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, in
   }
 }
 
+// Accumulator kept as PARTS partial sums (column blocks `part_stride` columns apart): several threads issue the MMAs
+// of a tile, each into a block of its own, and the sum is taken here in fp32, in block order.  `parts_written` (1 ..
+// PARTS) blocks hold data (a tile with fewer K steps than issuing threads leaves the others untouched).  Drains
+// `n_cols` columns (a multiple of 16, at most 128) and stores the first `valid` of them like drain_accumulator;
+// `release` is called once, after the last TMEM read.
+template <typename OutT, int PARTS, class Release>
+__device__ __forceinline__ void drain_partial_sums(uint32_t taddr, uint32_t part_stride, int parts_written, int n_cols,
+                                                   int valid, OutT* stage_warp, OutT* dst, int64_t ld, int lane,
+                                                   Release release, const RowScatter& scatter, int64_t first_row,
+                                                   int col_off, uint32_t* status) {
+  for (int c = 0; c < n_cols; c += 32) {
+    OutT* dest = nullptr;
+    if (scatter.meta != nullptr)
+      dest = scatter_row_ptr<OutT>(scatter, first_row + c + lane, c + lane < valid, ld, col_off, status);
+    uint32_t acc[32];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c0 = c + h * 16;
+      if (c0 < n_cols) {
+        uint32_t v[PARTS][16];
+#pragma unroll
+        for (int p = 0; p < PARTS; ++p)
+          if (p < parts_written) ptx::tc_ld_32x32b_x16(taddr + p * part_stride + c0, v[p]);   // warp-uniform
+        ptx::tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float sum = __uint_as_float(v[0][i]);
+#pragma unroll
+          for (int p = 1; p < PARTS; ++p)
+            if (p < parts_written) sum += __uint_as_float(v[p][i]);
+          acc[h * 16 + i] = __float_as_uint(sum);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[h * 16 + i] = 0u;
+      }
+    }
+    if (c + 32 >= n_cols) release();
+    store_chunk<OutT, 32>(acc, c, valid, stage_warp, dst, ld, lane, scatter, dest);
+  }
+}
+
 // The same for a warp that shares its lane quadrant with other warps: it takes the 32-column chunks first_chunk,
 // first_chunk + chunk_stride, ... and keeps one register set — the warps of a quadrant hide each other's TMEM
 // latency.  A warp without a chunk only calls `release`.

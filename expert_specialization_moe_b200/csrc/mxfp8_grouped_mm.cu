@@ -2,25 +2,46 @@
 //
 // Per expert e:  d[off_e + i, n] = sum_k a[off_e + i, k] * 2^(sfa-127) * b[e, n, k] * 2^(sfb-127), fp32 accumulate.
 //
+// This file: the two STREAMING shapes (experts with few rows, whose weights are read from HBM exactly once and
+// dominate the bytes) and the dispatcher that chains them with the CTA-pair kernel (mxfp8_grouped_mm_pair.cu).
+//
 // Mapping ("swap-AB"): the 128 rows of the tensor-core tile are 128 WEIGHT rows (output columns n), the token rows
 // of the expert sit on the MMA N axis.  N of tcgen05.mma can be any multiple of 16 up to 256, so a tile of an expert
 // with 3 tokens issues N=16 MMAs, one with 100 tokens N=112: the ragged dimension costs no padding to 128 and the
 // tail of an expert never needs a clipped tensor-map store.  Every tile streams a [128 x K] slab of the expert's
-// weights exactly once through a TMA ring (10 stages for tiles of at most 32 tokens, 6 stages for tiles of up to 128),
-// which is what bounds the layer (weights dominate the bytes).
+// weights once through a ring of 128-byte-wide K steps (10 slots of 21 KB for tiles of at most 32 tokens, 6 slots of
+// 31 KB for tiles of up to 112).
 //
-//   warp 0    producer: TMA loads (weights tile, token tile, two 512-byte scale atoms) per 128-wide K step
-//   warp 1    tensor memory allocation + MMA issue (one elected lane): scale atoms smem -> TMEM (tcgen05.cp),
-//             4 x tcgen05.mma (K=32 each) per K step, tcgen05.commit to free the stage / publish the accumulator
-//   warps 2-5 epilogue: tcgen05.ld accumulator (lane = output column, column = token) -> bf16/fp16 -> global,
-//             each warp store writes 64 contiguous bytes of one output row; double-buffered against the MMAs
+// What bounds such a tile is not the tensor pipe (a 128 x 32 x 32 MMA is 16 cycles of work) but two per-SM issue
+// limits, both measured on B200:
+//   * a tcgen05 instruction costs the THREAD that issues it ~180 cycles (mma) / ~65 cycles (cp), whatever its size.
+//     One thread issuing the four MMAs of every K step tops out at ~44 GB/s of weights per SM; the rate doubles with
+//     a second issuing thread.  Hence LANES threads issue the MMAs, thread l taking the K steps with kt % LANES == l
+//     into a partial accumulator of its own (the epilogue adds the partials), and the scale copies have two threads
+//     of their own;
+//   * what one SM pulls out of HBM through TMA is capped at ~55 GB/s whatever the box shape or the number of slots
+//     in flight; cp.async from 128 threads reaches ~63 GB/s, both together ~73-80 GB/s.  Hence the ODD ring slots are
+//     filled with cp.async (16-byte pieces written in the 128-byte swizzle pattern TMA would produce).
+// With both, ~90-110 SMs saturate HBM instead of all 148, and the rest can run the CTA-pair kernel of the same call
+// at the same time.
 //
-// Work list: tiles (expert, token tile of <=128, weight tile of 128) found with a per-CTA prefix scan over the
-// problem sizes (device resident: no host round trip).  The producer lane takes tile indices from the bucket's work
-// counter in the caller's scratch (atomicAdd; round-robin over the grid when the caller gave no scratch) and hands
-// each one to the MMA lane and the epilogue warps through a small shared-memory queue, so a CTA that starts late —
-// behind another kernel of the same call — just takes what is left.  Within an expert the token tile index runs
-// fastest so that CTAs working at the same time read the same weight slab (L2 reuse).
+//   warp 0      producer: per K step in an even slot, lanes 0..3 each issue ONE TMA load in the same instruction (weight
+//               tile, token tile, the two 512-byte scale atoms as records of their own tensor maps); lane 0 also takes
+//               the tile indices from the work counter and hands them to the other roles
+//   warp 1, 11-13  MMA issue, one lane each (as many as the shape has LANES): 4 x tcgen05.mma (K=32 each) per own K
+//               step, tcgen05.commit to free the slot / publish the accumulator; warp 1 also owns the TMEM allocation
+//   warps 2-5   epilogue: tcgen05.ld of the partial accumulators (lane = output column, column = token), fp32 sum,
+//               -> bf16/fp16 -> global through a shared-memory transpose, 128-bit stores; double-buffered against
+//               the MMAs of the next tile
+//   warps 6, 14 scale copies, one lane each: the slot's weight / token scale atom smem -> the slot's TMEM columns
+//               (tcgen05.cp), tcgen05.commit to the slot's sf_ready barrier
+//   warps 7-10  second load path: the odd ring slots by cp.async
+//
+// Work list: tiles (expert, weight tile of 128) found with a per-CTA prefix scan over the problem sizes (device
+// resident: no host round trip).  The producer takes tile indices from the bucket's work counter in the caller's
+// scratch (atomicAdd; round-robin over the grid when the caller gave no scratch) and hands each one to the other
+// roles through a small shared-memory queue, so a CTA that starts late — behind another kernel of the same call —
+// just takes what is left.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cstdlib>
@@ -35,42 +56,49 @@
 namespace es_b200 {
 namespace mm {
 
-constexpr int THREADS = 192;
+constexpr int THREADS = 480;           // 15 warps, see the role table above
+constexpr int COPY_WARP0 = 6, COPY_WARP1 = 14;
+constexpr int LOADER_WARP0 = 7;        // warps 7..10: cp.async loaders
+constexpr int LOADER_THREADS = 128;
+constexpr int MMA_WARP1 = 11;          // MMA lanes 1..3 sit in warps 11..13 (lane 0 in warp 1)
+constexpr int MAX_LANES = 4;
 constexpr int TILE_N = 128;     // weight rows per tile  (tcgen05.mma M)
-constexpr int TILE_K = 128;     // bytes of K per pipeline stage (one 128-byte swizzle atom)
+constexpr int TILE_K = 128;     // bytes of K per ring slot (one 128-byte swizzle atom)
 constexpr int W_BYTES = TILE_N * TILE_K;
 constexpr int SF_BYTES = 512;
 constexpr int MAX_STAGES = 10;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t SF_SLOT_COLS = 8;    // per ring slot: 4 columns of weight scales + 4 of token scales
 
-// Two tile shapes of the same kernel.  What bounds a streaming expert is how many weight bytes each SM keeps in
-// flight, i.e. the number of ring stages that fit the 227 KB of shared memory: experts with at most 32 rows need a
-// 4 KB token slot per stage and get 10 stages (160 KB of weights in flight), experts with up to 128 rows a 16 KB
-// slot and 6 stages.
-template <int TOK_TILE_, int STAGES_>
+// A streaming shape: experts with at most TOK_TILE rows (ONE token tile per expert: the tile's token scales are then
+// exactly one 128-row atom), STAGES ring slots, LANES MMA-issuing threads = partial accumulators.
+template <int TOK_TILE_, int STAGES_, int LANES_>
 struct Shape {
   static constexpr int TOK_TILE = TOK_TILE_;     // token rows per tile (tcgen05.mma N, runtime multiple of 16)
   static constexpr int STAGES = STAGES_;
+  static constexpr int LANES = LANES_;
   static constexpr int X_BYTES = TOK_TILE * TILE_K;
-  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // a multiple of 1024
-  static_assert(STAGE_BYTES % 1024 == 0 && STAGES <= MAX_STAGES, "stage layout");
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // W | X | weight scales | token scales
+  static constexpr uint32_t ACC_COLS = LANES * TOK_TILE;                 // one accumulator buffer: LANES partials
+  static constexpr uint32_t SF_COL0 = 2 * ACC_COLS;                      // two buffers, then the scale slots
+  static_assert(STAGE_BYTES % 1024 == 0 && STAGES <= MAX_STAGES && STAGES % 2 == 0, "ring layout");
+  static_assert(TOK_TILE % 16 == 0 && TOK_TILE <= 128 && (LANES == 1 || LANES == 2 || LANES == 4), "tile shape");
+  static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 };
-using ShapeTiny = Shape<32, 10>;     // 21 KB stages
-using ShapeMid = Shape<128, 6>;      // 33 KB stages
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t ACC_COLS = 128;      // two accumulators: columns [0,128) and [128,256)
-constexpr uint32_t SFW_COL = 256;       // 4 columns: scales of the weight tile
-constexpr uint32_t SFX_COL = 260;       // 4 columns: scales of the token tile
+using ShapeTiny = Shape<32, 10, 4>;   // 21 KB slots; TMEM: 2 x 4 x 32 accumulator columns + 80 scale columns
+using ShapeMid = Shape<112, 6, 2>;    // 31 KB slots; TMEM: 2 x 2 x 112 accumulator columns + 48 scale columns
 
-constexpr uint32_t ERR_PRODUCER = 1u, ERR_MMA = 2u, ERR_EPILOGUE = 4u;
+constexpr uint32_t ERR_PRODUCER = 1u, ERR_MMA = 2u, ERR_EPILOGUE = 4u, ERR_SCALE_COPY = 8u, ERR_LOADER = 0x400u;
 constexpr int QUEUE_DEPTH = 4;          // tile indices in flight between the producer lane and the other roles
 
 struct SharedCtl {
-  uint64_t full[MAX_STAGES];
-  uint64_t empty[MAX_STAGES];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t full[MAX_STAGES];            // even slots: 1 arrive.expect_tx + bytes; odd slots: one arrival per loader thread
+  uint64_t empty[MAX_STAGES];           // 1 arrival: the commit of the MMA lane that owns the K step
+  uint64_t sf_ready[MAX_STAGES];        // 2 arrivals: both scale atoms of the slot are in its TMEM columns
+  uint64_t tmem_full[2];                // LANES arrivals: every MMA lane's share of the tile is complete
+  uint64_t tmem_empty[2];               // 4 arrivals: the epilogue warps have read the buffer
   uint64_t q_full[QUEUE_DEPTH];         // 1 arrival: the producer lane has written q_tile[slot]
-  uint64_t q_empty[QUEUE_DEPTH];        // 5 arrivals: the MMA lane and the four epilogue warps have read it
+  uint64_t q_empty[QUEUE_DEPTH];        // every consuming role has read it
   int q_tile[QUEUE_DEPTH];              // tile index, or -1: no more work
   uint32_t tmem_base;
   int abort_flag;
@@ -86,47 +114,61 @@ constexpr size_t smem_bytes() {
 __device__ uint32_t g_status = 0;   // sticky error bits of the grouped GEMM kernels (bounded waits that gave up)
 
 struct TileInfo {
-  int e, tt, nt;
-  int valid;     // token rows of this tile that belong to the expert
+  int e, nt;
+  int valid;     // token rows of the expert (= of this tile)
   int n_mma;     // valid rounded up to 16
   int row0;      // first token row in a / d
 };
 
-template <int TOK_TILE>
+// tile t of this launch -> (expert, weight tile); one token tile per expert
 __device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
                                                 const int* expert_offsets) {
   TileInfo ti;
   ti.e = upper_bound_expert(prefix, num_experts, t);
-  const int i = t - prefix[ti.e];
-  const int m = problem_sizes[ti.e * 3];
-  const int token_tiles = (m + TOK_TILE - 1) / TOK_TILE;
-  ti.nt = i / token_tiles;
-  ti.tt = i - ti.nt * token_tiles;
-  const int rem = m - ti.tt * TOK_TILE;
-  ti.valid = rem < TOK_TILE ? rem : TOK_TILE;
+  ti.nt = t - prefix[ti.e];
+  ti.valid = problem_sizes[ti.e * 3];
   ti.n_mma = (ti.valid + 15) & ~15;
-  ti.row0 = expert_offsets[ti.e] + ti.tt * TOK_TILE;
+  ti.row0 = expert_offsets[ti.e];
   return ti;
 }
 
-template <typename OutT>
-__device__ __forceinline__ OutT from_f32(float v);
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+// One consumer of the tile queue: waits for the slot, reads the index, reports the slot read.  `whole_warp`: all 32
+// lanes call it together (one arrival per warp), otherwise a single lane.
+struct QueueReader {
+  int qs = 0;
+  uint32_t qph = 0;
+  template <bool whole_warp>
+  __device__ __forceinline__ bool next(SharedCtl* ctl, volatile int* abort_flag, int lane, int* t) {
+    bool have = ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag);
+    if (whole_warp) have = __all_sync(0xffffffffu, have);
+    if (!have) return false;
+    *t = ctl->q_tile[qs];
+    if (whole_warp) {
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&ctl->q_empty[qs]);
+    } else {
+      ptx::mbar_arrive(&ctl->q_empty[qs]);
+    }
+    if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+    return true;
+  }
+};
 
 template <typename OutT, class S>
 __global__ void __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
                         const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
-                        const __grid_constant__ CUtensorMap map_x128, const uint8_t* __restrict__ sf_tokens,
-                        const uint8_t* __restrict__ sf_weights, OutT* __restrict__ d,
-                        const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                        const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
-                        int max_rows, int wait_at_start, const __grid_constant__ RowScatter scatter,
-                        uint32_t* counters, int bucket, int last_of_call, uint32_t earlier_ctas) {
+                        const __grid_constant__ CUtensorMap map_xt, const __grid_constant__ CUtensorMap map_sfx,
+                        const __grid_constant__ CUtensorMap map_sfw, const uint8_t* __restrict__ a_codes,
+                        const uint8_t* __restrict__ w_codes, const uint8_t* __restrict__ sf_tokens,
+                        const uint8_t* __restrict__ sf_weights, int num_rows, long long sf_token_bytes, int use_lsu,
+                        OutT* __restrict__ d, const int* __restrict__ problem_sizes,
+                        const int* __restrict__ expert_offsets, const int* __restrict__ blockscale_offsets,
+                        int num_experts, int n, int k, int min_rows, int max_rows, int wait_at_start,
+                        const __grid_constant__ RowScatter scatter, uint32_t* counters, int bucket, int last_of_call,
+                        uint32_t earlier_ctas) {
   constexpr int TOK_TILE = S::TOK_TILE, STAGES = S::STAGES, X_BYTES = S::X_BYTES, STAGE_BYTES = S::STAGE_BYTES;
+  constexpr int LANES = S::LANES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 4 x 2 KB, one per epilogue warp
@@ -136,16 +178,18 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      ptx::mbar_init(&ctl->full[s], 1);
+      ptx::mbar_init(&ctl->full[s], (use_lsu && (s & 1)) ? LOADER_THREADS : 1);
       ptx::mbar_init(&ctl->empty[s], 1);
+      ptx::mbar_init(&ctl->sf_ready[s], 2);
     }
     for (int a = 0; a < 2; ++a) {
-      ptx::mbar_init(&ctl->tmem_full[a], 1);
-      ptx::mbar_init(&ctl->tmem_empty[a], 4);   // one arrival per epilogue warp
+      ptx::mbar_init(&ctl->tmem_full[a], LANES);
+      ptx::mbar_init(&ctl->tmem_empty[a], 4);
     }
     for (int q = 0; q < QUEUE_DEPTH; ++q) {
       ptx::mbar_init(&ctl->q_full[q], 1);
-      ptx::mbar_init(&ctl->q_empty[q], 5);
+      // readers: LANES MMA lanes, 2 copy lanes, 4 epilogue warps, and the 4 loader warps when they run
+      ptx::mbar_init(&ctl->q_empty[q], LANES + 2 + 4 + (use_lsu ? LOADER_THREADS / 32 : 0));
     }
     ctl->abort_flag = 0;
     ptx::fence_mbar_init();
@@ -153,7 +197,9 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     ptx::prefetch_tensormap(&map_x16);
     ptx::prefetch_tensormap(&map_x32);
     ptx::prefetch_tensormap(&map_x64);
-    ptx::prefetch_tensormap(&map_x128);
+    ptx::prefetch_tensormap(&map_xt);
+    ptx::prefetch_tensormap(&map_sfx);
+    ptx::prefetch_tensormap(&map_sfw);
   }
   if (warp == 1) {
     ptx::tmem_alloc(&ctl->tmem_base, TMEM_COLS);
@@ -165,7 +211,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   // start on SMs as they become free; stream order for what follows the call is kept at the end (end_of_kernel).
   if (wait_at_start) pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
-  // this launch owns the experts with min_rows <= rows <= max_rows
+  // this launch owns the experts with min_rows <= rows <= max_rows (<= TOK_TILE)
   // (an expert whose scales do not start on a 128-row atom cannot be addressed: reported and skipped)
   block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
@@ -174,7 +220,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       atomicOr(&g_status, ERR_SCALE_OFFSET_BIT);
       return 0;
     }
-    return ((m + TOK_TILE - 1) / TOK_TILE) * n_tiles;
+    return n_tiles;
   });
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -184,148 +230,247 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   const uint32_t tmem_base = ctl->tmem_base;
   const int total_tiles = ctl->tile_prefix[num_experts];
   const int kt_count = k / TILE_K;
-  const int64_t sf_row_bytes = k / 32;
   volatile int* abort_flag = &ctl->abort_flag;
+  const int mma_lane = warp == 1 ? 0 : (warp >= MMA_WARP1 && warp < MMA_WARP1 + MAX_LANES - 1) ? warp - MMA_WARP1 + 1 : -1;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ producer
-    if (lane == 0) {
-      int s = 0, qs = 0;
-      uint32_t ph = 0, qph = 0;
-      bool ok = true;
-      uint32_t* counter = counters ? counters + bucket : nullptr;
-      int t = counter ? (int)atomicAdd(counter, 1u) : (int)blockIdx.x;
-      while (ok) {
-        // hand the tile index (or the end mark) to the other roles
-        if (!ptx::mbar_wait(&ctl->q_empty[qs], qph ^ 1u, abort_flag)) {
+    // ------------------------------------------------------------------ producer (whole warp walks the work list)
+    int s = 0, qs = 0;
+    uint32_t ph = 0, qph = 0;
+    uint32_t* counter = counters ? counters + bucket : nullptr;
+    int t_mine = 0;                   // lane 0: the index that goes out next
+    if (lane == 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : (int)blockIdx.x;
+    while (true) {
+      // lane 0 hands the tile index (or the end mark) to the other roles
+      int t = -1;
+      bool q_ok = true;
+      if (lane == 0) {
+        q_ok = ptx::mbar_wait(&ctl->q_empty[qs], qph ^ 1u, abort_flag);
+        if (q_ok) {
+          t = t_mine < total_tiles ? t_mine : -1;
+          ctl->q_tile[qs] = t;
+          ptx::mbar_arrive(&ctl->q_full[qs]);
+          // the next index is requested now; its round trip to L2 hides behind this tile's loads
+          if (t >= 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : t_mine + (int)gridDim.x;
+        }
+      }
+      q_ok = __shfl_sync(0xffffffffu, (int)q_ok, 0) != 0;
+      t = __shfl_sync(0xffffffffu, t, 0);
+      if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+      if (!q_ok) {
+        if (lane == 0) {
           *abort_flag = 1;
           atomicOr(&g_status, ERR_PRODUCER);
-          break;
         }
-        const bool live = t < total_tiles;
-        ctl->q_tile[qs] = live ? t : -1;
-        ptx::mbar_arrive(&ctl->q_full[qs]);
-        if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
-        if (!live) break;
-        // the next index is requested now; its round trip to L2 hides behind this tile's loads
-        const int t_next = counter ? (int)atomicAdd(counter, 1u) : t + (int)gridDim.x;
-        const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-        const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_x128;
-        const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : 128u;
-        const uint32_t tx = W_BYTES + box_rows * TILE_K + 2 * SF_BYTES;
-        const uint8_t* sfw = sf_weights + (int64_t)ti.e * n * sf_row_bytes + (int64_t)ti.nt * kt_count * SF_BYTES;
-        const uint8_t* sfx = sf_tokens + (int64_t)blockscale_offsets[ti.e] * sf_row_bytes + (int64_t)ti.tt * kt_count * SF_BYTES;
-        const int w_row = ti.e * n + ti.nt * TILE_N;
-        for (int kt = 0; kt < kt_count; ++kt) {
-          if (!ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag)) {
-            ok = false;
-            *abort_flag = 1;
-            atomicOr(&g_status, ERR_PRODUCER);
-            break;
-          }
+        break;
+      }
+      if (t < 0) break;
+      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_xt;
+      const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : (uint32_t)TOK_TILE;
+      const uint32_t tx = W_BYTES + box_rows * TILE_K + 2 * SF_BYTES;
+      // this lane's load: 0 weight tile (streamed once: evict first), 1 token tile (re-read by every weight tile of
+      // the expert: evict last), 2 weight scale atom, 3 token scale atom (512-byte records, index = atom number)
+      const int sfw_atom = (ti.e * n_tiles + ti.nt) * kt_count;
+      const int sfx_atom = (blockscale_offsets[ti.e] >> 7) * kt_count;
+      const CUtensorMap* my_map = lane == 0 ? &map_w : lane == 1 ? xm : lane == 2 ? &map_sfw : &map_sfx;
+      const uint32_t my_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)W_BYTES
+                              : lane == 2 ? (uint32_t)(W_BYTES + X_BYTES) : (uint32_t)(W_BYTES + X_BYTES + SF_BYTES);
+      const int my_c1 = lane == 0 ? ti.e * n + ti.nt * TILE_N : lane == 1 ? ti.row0 : lane == 2 ? sfw_atom : sfx_atom;
+      const uint64_t my_hint = lane == 0 ? ptx::kL2EvictFirst : lane == 1 ? ptx::kL2EvictLast : ptx::kL2EvictNormal;
+      bool ok = true;
+      for (int kt = 0; kt < kt_count; ++kt) {
+        if (!(use_lsu && (s & 1))) {          // odd slots belong to the cp.async loaders
+          ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag));
+          if (!ok) break;
           uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
-          ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
-          ptx::tma_load_2d(stage, &map_w, &ctl->full[s], kt * TILE_K, w_row);
-          ptx::tma_load_2d(stage + W_BYTES, xm, &ctl->full[s], kt * TILE_K, ti.row0);
-          ptx::bulk_load(stage + W_BYTES + X_BYTES, sfw + (int64_t)kt * SF_BYTES, SF_BYTES, &ctl->full[s]);
-          ptx::bulk_load(stage + W_BYTES + X_BYTES + SF_BYTES, sfx + (int64_t)kt * SF_BYTES, SF_BYTES, &ctl->full[s]);
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
+          if (lane == 0) ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
+          __syncwarp();
+          if (lane < 4)
+            ptx::tma_load_2d_hint(stage + my_off, my_map, &ctl->full[s], lane < 2 ? kt * TILE_K : 0,
+                                  lane < 2 ? my_c1 : my_c1 + kt, my_hint);
         }
-        t = t_next;
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+      if (!ok) {
+        if (lane == 0) {
+          *abort_flag = 1;
+          atomicOr(&g_status, ERR_PRODUCER);
+        }
+        break;
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
-      int s = 0, qs = 0;
-      uint32_t ph = 0, qph = 0;
+  } else if (mma_lane >= 0) {
+    // ------------------------------------------------------------------ MMA issue: lane l of LANES takes the K steps
+    // with kt % LANES == l and accumulates them in partial accumulator l of the tile's buffer
+    if (lane == 0 && mma_lane < LANES) {
+      QueueReader q;
+      int s = 0;
+      uint32_t ph = 0;
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
-      const uint32_t sfw_t = tmem_base + SFW_COL;
-      const uint32_t sfx_t = tmem_base + SFX_COL;
       while (ok) {
-        if (!ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag)) {
-          *abort_flag = 1;
-          atomicOr(&g_status, ERR_MMA);
-          break;
-        }
-        const int t = ctl->q_tile[qs];
-        ptx::mbar_arrive(&ctl->q_empty[qs]);
-        if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+        int t;
+        if (!q.next<false>(ctl, abort_flag, lane, &t)) { ok = false; break; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
-        if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) { ok = false; }
+        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
-        for (int kt = 0; ok && kt < kt_count; ++kt) {
-          if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
-          const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
-          ptx::tc_cp_sf(sfw_t, ptx::make_desc_sf(stage + W_BYTES + X_BYTES));
-          ptx::tc_cp_sf(sfx_t, ptx::make_desc_sf(stage + W_BYTES + X_BYTES + SF_BYTES));
-          const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
-          const uint64_t b_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
+        const uint32_t d_tmem = tmem_base + acc * S::ACC_COLS + mma_lane * TOK_TILE;
+        for (int kt = 0; kt < kt_count; ++kt) {
+          if ((kt & (LANES - 1)) == mma_lane) {
+            if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
+            if (!ptx::mbar_wait(&ctl->sf_ready[s], ph, abort_flag)) { ok = false; break; }
+            if (use_lsu && (s & 1)) ptx::fence_proxy_async_shared();   // slot written by cp.async (generic proxy)
+            ptx::tc_fence_after_sync();
+            const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
+            const uint32_t sfw_t = tmem_base + S::SF_COL0 + s * SF_SLOT_COLS;
+            const uint32_t sfx_t = sfw_t + 4;
+            const uint64_t a_desc = ptx::make_desc_k_sw128(stage);
+            const uint64_t b_desc = ptx::make_desc_k_sw128(stage + W_BYTES);
 #pragma unroll
-          for (uint32_t j = 0; j < 4; ++j) {
-            ptx::tc_mma_mxf8(d_tmem, a_desc + 2 * j, b_desc + 2 * j, ptx::make_idesc_mxf8(TILE_N, ti.n_mma, j, j),
-                             sfw_t | (j << 30), sfx_t | (j << 30), (kt | j) != 0 ? 1u : 0u);
+            for (uint32_t j = 0; j < 4; ++j)      // the lane's first MMA of the tile overwrites its partial
+              ptx::tc_mma_mxf8(d_tmem, a_desc + 2 * j, b_desc + 2 * j, ptx::make_idesc_mxf8(TILE_N, ti.n_mma, j, j),
+                               sfw_t | (j << 30), sfx_t | (j << 30), (kt == mma_lane && j == 0) ? 0u : 1u);
+            ptx::tc_commit(&ctl->empty[s]);       // slot reusable once these MMAs have read it
           }
-          ptx::tc_commit(&ctl->empty[s]);      // stage reusable once these MMAs have read it
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        if (!ok) {
-          *abort_flag = 1;
-          atomicOr(&g_status, ERR_MMA);
-          break;
-        }
-        ptx::tc_commit(&ctl->tmem_full[acc]);  // accumulator complete
+        if (!ok) break;
+        ptx::tc_commit(&ctl->tmem_full[acc]);     // this lane's share of the accumulator is complete
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(&g_status, ERR_MMA);
+      }
     }
-  } else {
+  } else if (warp == COPY_WARP0 || warp == COPY_WARP1) {
+    // ------------------------------------------------------------------ scale copies: warp 6 the weight atom, warp 14
+    // the token atom of every slot.  A slot's TMEM columns are rewritten only after the slot was refilled, i.e. after
+    // the MMAs that read them have completed (their commit released the slot to the producer).
+    if (lane == 0) {
+      const int which = warp == COPY_WARP0 ? 0 : 1;
+      QueueReader q;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      while (ok) {
+        int t;
+        if (!q.next<false>(ctl, abort_flag, lane, &t)) { ok = false; break; }
+        if (t < 0) break;
+        for (int kt = 0; kt < kt_count; ++kt) {
+          if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
+          if (use_lsu && (s & 1)) ptx::fence_proxy_async_shared();
+          ptx::tc_fence_after_sync();
+          const uint32_t sf_smem = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES) + W_BYTES + X_BYTES + which * SF_BYTES;
+          ptx::tc_cp_sf(tmem_base + S::SF_COL0 + s * SF_SLOT_COLS + which * 4, ptx::make_desc_sf(sf_smem));
+          ptx::tc_commit(&ctl->sf_ready[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(&g_status, ERR_SCALE_COPY);
+      }
+    }
+  } else if (warp >= LOADER_WARP0 && warp < LOADER_WARP0 + LOADER_THREADS / 32) {
+    // ------------------------------------------------------------------ second load path (warps 7..10, cp.async)
+    // Fills the odd ring slots.  Per slot a thread copies 8 pieces of the weight tile, its share of the token tile
+    // and one piece of the two scale atoms (16 bytes each); the slot's barrier counts one arrival per loader thread,
+    // made by the hardware when that thread's copies have landed (cp.async.mbarrier.arrive.noinc), so a thread never
+    // waits for its own copies and keeps as many slots in flight as the ring has free.  The consumers of a cp.async
+    // slot (MMA lanes, copy lanes) issue a proxy fence after their wait: the data was written through the generic
+    // proxy and is read by tcgen05 through the async proxy.
+    if (use_lsu) {
+      const int lt = threadIdx.x - LOADER_WARP0 * 32;        // 0..127
+      const int c16 = lt & 7, r0 = lt >> 3;                   // this thread's 16-byte column and first row
+      QueueReader q;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      while (ok) {
+        int t;
+        if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
+        if (t < 0) break;
+        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const uint8_t* w_src = w_codes + ((int64_t)ti.e * n + ti.nt * TILE_N + r0) * k + c16 * 16;
+        const uint8_t* x_src = a_codes + ((int64_t)ti.row0 + r0) * k + c16 * 16;
+        const int64_t sfw_off = ((int64_t)(ti.e * n_tiles + ti.nt) * kt_count) * SF_BYTES;
+        const int64_t sfx_off = ((int64_t)(blockscale_offsets[ti.e] >> 7) * kt_count) * SF_BYTES;
+        // the two scale atoms are 64 pieces: threads 0..31 the weight atom, 32..63 the token atom (zeros past the buffer)
+        const uint8_t* sf_src = lt < 32 ? sf_weights + sfw_off + lt * 16 : sf_tokens + sfx_off + (lt - 32) * 16;
+        const bool sf_in_range = lt < 32 || sfx_off + (int64_t)kt_count * SF_BYTES <= sf_token_bytes;
+        const uint32_t dst_swz = (uint32_t)(r0 * 128 + ((c16 ^ (r0 & 7)) << 4));   // row r0 + 16 j keeps (r & 7)
+        for (int kt = 0; kt < kt_count; ++kt) {
+          if (s & 1) {
+            ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag));
+            if (!ok) break;
+            const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              ptx::cp_async_16_hint(stage + dst_swz + j * 2048, w_src + (int64_t)j * 16 * k + kt * TILE_K,
+                                    ptx::kL2EvictFirst);      // weights are read once
+#pragma unroll
+            for (int j = 0; j < TOK_TILE / 16; ++j) {
+              const int r = r0 + 16 * j;
+              if (r < ti.n_mma) {
+                const bool in_range = ti.row0 + r < num_rows;       // rows past the end of `a` read as zeros
+                ptx::cp_async_16(stage + W_BYTES + dst_swz + j * 2048,
+                                 in_range ? x_src + (int64_t)j * 16 * k + kt * TILE_K : a_codes, in_range ? 16u : 0u);
+              }
+            }
+            if (lt < 64)
+              ptx::cp_async_16(stage + W_BYTES + X_BYTES + lt * 16,
+                               sf_in_range ? sf_src + (int64_t)kt * SF_BYTES : sf_weights, sf_in_range ? 16u : 0u);
+            ptx::cp_async_arrive_noinc(&ctl->full[s]);
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok && lane == 0) {
+        *abort_flag = 1;
+        atomicOr(&g_status, ERR_LOADER);
+      }
+    }
+  } else if (warp >= 2 && warp <= 5) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int q = warp & 3;   // TMEM lane quadrant this warp may access
-    int acc = 0, qs = 0;
-    uint32_t acc_ph = 0, qph = 0;
-    while (true) {
-      const bool have = ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag);
-      if (!__all_sync(0xffffffffu, have)) {
-        if (lane == 0) {
-          *abort_flag = 1;
-          atomicOr(&g_status, ERR_EPILOGUE);
-        }
-        break;
-      }
-      const int t = ctl->q_tile[qs];
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&ctl->q_empty[qs]);
-      if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
+    const int quad = warp & 3;   // TMEM lane quadrant this warp may access
+    QueueReader q;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    while (ok) {
+      int t;
+      if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
       if (t < 0) break;
-      const TileInfo ti = decode_tile<TOK_TILE>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
       const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) {
-        if (lane == 0) {
-          *abort_flag = 1;
-          atomicOr(&g_status, ERR_EPILOGUE);
-        }
-        break;
-      }
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
-      OutT* dst = d + (int64_t)ti.row0 * n + (ti.nt * TILE_N + q * 32);
-      drain_accumulator<OutT>(taddr, ti.n_mma, ti.valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, dst, n,
-                              true, lane, [&] {
-                                // all of this warp's accumulator reads are done: hand the buffer back to the MMA warp
-                                ptx::tc_fence_before_sync();
-                                __syncwarp();
-                                if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
-                              }, scatter, ti.row0, ti.nt * TILE_N + q * 32, &g_status);
+      const uint32_t taddr = tmem_base + acc * S::ACC_COLS + ((uint32_t)(quad * 32) << 16);
+      OutT* dst = d + (int64_t)ti.row0 * n + (ti.nt * TILE_N + quad * 32);
+      drain_partial_sums<OutT, LANES>(
+          taddr, TOK_TILE, kt_count < LANES ? kt_count : LANES, ti.n_mma, ti.valid,
+          reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, dst, n, lane,
+          [&] {
+            // all of this warp's accumulator reads are done: hand the buffer back to the MMA lanes
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+          },
+          scatter, ti.row0, ti.nt * TILE_N + quad * 32, &g_status);
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
     }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicOr(&g_status, ERR_EPILOGUE);
+    }
   }
+  // (warps of MMA lanes the shape does not use fall through)
 
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -349,11 +494,20 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
   CUtensorMap map_w, map_x[4];
   rc = make_tensormap_u8_sw128(&map_w, c.b, (uint64_t)c.num_experts * c.n, (uint64_t)c.k, TILE_N);
   if (rc != ES_B200_OK) return rc;
-  const uint32_t boxes[4] = {16, 32, 64, 128};
+  const uint32_t boxes[4] = {16, 32, 64, (uint32_t)TOK_TILE};   // token boxes; the last one is the shape's full tile
   for (int i = 0; i < 4; ++i) {
     rc = make_tensormap_u8_sw128(&map_x[i], c.a, (uint64_t)c.num_rows, (uint64_t)c.k, boxes[i]);
     if (rc != ES_B200_OK) return rc;
   }
+
+  CUtensorMap map_sfx, map_sfw;
+  const int kt_count = c.k / TILE_K;
+  rc = make_tensormap_records512(&map_sfw, c.sfb, (uint64_t)c.num_experts * (c.n / TILE_N) * kt_count);
+  if (rc != ES_B200_OK) return rc;
+  // whole 128-row atoms only; loads past the end read as zero (a map needs at least one record)
+  const uint64_t sfx_records = (uint64_t)(c.sfa_rows / 128) * kt_count;
+  rc = make_tensormap_records512(&map_sfx, c.sfa, sfx_records ? sfx_records : 1);
+  if (rc != ES_B200_OK) return rc;
 
   auto kernel = mxfp8_grouped_mm_kernel<OutT, S>;
   static bool configured[64] = {false};   // per device (one static per instantiation)
@@ -363,8 +517,8 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
     ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     configured[dev & 63] = true;
   }
-  // upper bound of the tile count known on the host: full token tiles of num_rows plus one partial per expert
-  const int64_t max_tiles = ((c.num_rows + TOK_TILE - 1) / TOK_TILE + c.num_experts) * (int64_t)(c.n / TILE_N);
+  // upper bound of the tile count known on the host: one token tile per expert
+  const int64_t max_tiles = (int64_t)c.num_experts * (c.n / TILE_N);
   int grid = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
   const int cap = tunables().mm_stream_max_ctas;
   if (cap > 0 && grid > cap) grid = cap;
@@ -379,7 +533,10 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], c.sfa, c.sfb,
+  const int use_lsu = tunables().mm_stream_lsu ? 1 : 0;
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], map_sfx, map_sfw,
+                                 static_cast<const uint8_t*>(c.a), static_cast<const uint8_t*>(c.b), c.sfa, c.sfb,
+                                 (int)c.num_rows, (long long)(c.sfa_rows * (c.k / 32)), use_lsu,
                                  static_cast<OutT*>(c.d), c.ps, c.eo, c.bo, c.num_experts, c.n, c.k, min_rows, max_rows,
                                  first_of_call ? 1 : 0, *c.scatter, c.counters, bucket, last_of_call ? 1 : 0,
                                  *earlier_ctas));
@@ -432,9 +589,9 @@ static int grouped_mm_impl(const void* a, const void* b, const uint8_t* sfa, con
   // Tile-shape specialisation.  Problem sizes live on the device, so the host cannot bucket the experts; instead
   // one kernel per row-count bucket is launched, back to back on the caller's stream with programmatic dependent
   // launch, and each one filters the experts by row count inside its own work-list scan:
-  //   rows <= tiny_max  : single-CTA kernel, 128 weights x <=32 tokens, 10-stage ring  \  these experts stream their
-  //   rows <  heavy_min : single-CTA kernel, 128 weights x <=128 tokens, 6-stage ring  /  weights from HBM exactly
-  //                       once; what counts is weight bytes in flight;
+  //   rows <= tiny_max  : single-CTA kernel, 128 weights x <=32 tokens, 10-slot ring   \  these experts stream their
+  //   rows <  heavy_min : single-CTA kernel, 128 weights x <=112 tokens, 6-slot ring   /  weights from HBM exactly
+  //                       once; what counts is weight bytes per second and SM;
   //   rows >= heavy_min : CTA-pair kernel, 256 weights x <=384 tokens, weight-stationary K step — these experts
   //                       re-read operands from L2, what counts is operand bytes per FLOP.
   // A kernel whose bucket is empty exits after its scan.  A bucket that even the host-known upper bound of rows per
@@ -450,9 +607,12 @@ static int grouped_mm_impl(const void* a, const void* b, const uint8_t* sfa, con
   // kernels queued behind it.
   const Tunables& tn = tunables();
   const BucketThresholds table = bucket_thresholds(n, k);
-  int heavy_min = tn.mm_heavy_min_rows > 0 ? tn.mm_heavy_min_rows : tn.mm_heavy_min_rows < 0 ? 0x7fffffff : table.heavy_min_rows;
+  // (a streaming shape holds a whole expert in one token tile, so the CTA-pair kernel takes everything above the
+  // larger shape's tile)
+  int heavy_min = tn.mm_heavy_min_rows > 0 ? tn.mm_heavy_min_rows : table.heavy_min_rows;
+  if (heavy_min > mm::ShapeMid::TOK_TILE + 1) heavy_min = mm::ShapeMid::TOK_TILE + 1;
   int tiny_max = tn.mm_tiny_max_rows > 0 ? tn.mm_tiny_max_rows : table.tiny_max_rows;
-  if (tiny_max > 32) tiny_max = 32;
+  if (tiny_max > mm::ShapeTiny::TOK_TILE) tiny_max = mm::ShapeTiny::TOK_TILE;
   if (tiny_max > heavy_min - 1) tiny_max = heavy_min - 1;
   const bool bf16 = out_dtype == ES_B200_BF16;
   mm::CallArgs c = {a, b, sfa, sfb, d, problem_sizes, expert_offsets, blockscale_offsets, num_experts, num_rows, n, k,

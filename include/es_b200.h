@@ -231,7 +231,7 @@ int es_b200_ep_route_count_static(const void* topk_ids, int ids_are_int64, int p
  * Tunables of the tile-shape dispatcher (no counterpart in the reference, whose bucket rules are compile-time
  * functors: es_fp8_blockwise_functor.cuh:122-256).  Process-wide; each also has an environment override read once,
  * ES_B200_<NAME IN CAPITALS>.  Names: "mm_heavy_min_rows" (experts with at least this many rows use CTA-pair tiles;
- * 0 = per-(n, k) table, negative = never), "mm_tiny_max_rows" (0 = table), "mm_pair_first_clusters",
+ * 0 = per-(n, k) table; at most 113), "mm_tiny_max_rows" (0 = table), "mm_pair_first_clusters",
  * "mm_split_min_rows", "mm_stream_max_ctas", "mm_pair_max_clusters" (grid shaping of a split call, 0 = no cap),
  * "mm_dynamic" (0: ignore the work counters).  Unknown name: ES_B200_ERR_INVALID_ARGUMENT.
  */

@@ -124,11 +124,13 @@ def _worker_fused(rank, world, port, q):
                 if fuse:
                     assert torch.equal(out, out_unfused), "fused and unfused combine differ"
                 out_unfused = out
-        # the same layer as two half-batches on two streams: per-row results do not depend on the batching
+        # the same layer as two half-batches on two streams: the same values up to fp32 summation order (an expert's
+        # rows split in two may fall into another row-count bucket, which adds its partial accumulators differently)
         px = ep.PipelinedExchange(E, topk, tokens, H, dev)
         out_p = px.forward(x, ids, wts, shard)
         torch.cuda.synchronize()
-        assert torch.equal(out_p, out), "pipelined and single-stream exchange differ"
+        d_p = float((out_p.float() - out.float()).abs().max() / out.float().abs().max().clamp_min(1e-6))
+        assert d_p < 1e-2, f"pipelined and single-stream exchange differ by {d_p}"
         raw = ctypes.c_uint32(0)
         rc = _cabi.load().es_b200_check_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(raw))
         q.put((rank, worst if rc == 0 else float("inf"), None))

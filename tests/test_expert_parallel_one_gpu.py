@@ -93,9 +93,11 @@ def test_fused_exchange_layer_on_one_gpu(group_of_one):
             assert diff < 5e-3, f"fuse_combine={fuse}: calc_diff {diff}"
             outs.append(out)
         assert torch.equal(outs[0], outs[1]), "combine kernel and scatter epilogue disagree"
+        # two half-batches: an expert's rows split in two may fall into another row-count bucket, whose kernel adds its
+        # partial accumulators in another order — same values up to fp32 summation order
         out_p = px.forward(x, ids, wts, shard)
         torch.cuda.synchronize()
-        assert torch.equal(out_p, outs[1]), "two half-batches on two streams disagree with one batch"
+        assert calc_diff(out_p.float().cpu(), outs[1].float().cpu()) < 1e-5, "two half-batches disagree with one batch"
     rc, raw = _status(lib, dev)
     assert rc == 0, f"device status {raw:#x}"
 
