@@ -69,6 +69,9 @@ WORKLOADS = {
     "ref_dist_ep8": (32, None, 4096, 7168, "MXFP8 grouped GEMM on the reference's SM100 benchmark: DeepSeek-R1 gate_up "
                                            "EP8 decode (n=4096, k=7168, E=32), row counts 70/15/10/5 % from "
                                            "1-32/32-64/64-128/128-1024"),
+    # weight-streaming probe: 128 experts of 1..32 rows, every tile streams a [128 x 7168] slab once; with
+    # --tunable mm_stream_max_ctas=<n> it gives the per-SM ingest rate of the streaming kernel at n CTAs
+    "stream_probe": (128, None, 4096, 7168, "weight-streaming probe: E=128 experts of 1..32 rows (uniform), N=4096, K=7168"),
     "quant_small": (64, 8192, 0, 7168, "grouped MXFP8 quantisation at 1/4 scale for profiler captures: bf16 "
                                        "[8192, 7168], E=64"),
 }
@@ -100,6 +103,8 @@ def workload_counts(name):
         return np.full(E, T // E, dtype=np.int64)
     if name.startswith("ref_dist"):
         return ref_dist_counts(E)
+    if name == "stream_probe":
+        return np.random.default_rng(0).integers(1, 33, size=E).astype(np.int64)
     return zipf_counts(T, E, 1.2, 0)
 
 
@@ -759,6 +764,9 @@ def main():
                     help="expert-to-GPU placement for N > 1 (default load_balanced): contiguous blocks of E/N experts; "
                          "E/N experts per GPU chosen greedily by rows; or load-aware with the hottest expert "
                          "replicated (see place_experts)")
+    ap.add_argument("--tunable", action="append", default=[], metavar="NAME=VALUE",
+                    help="set a dispatcher tunable of the library before the run (es_b200_set_tunable), e.g. "
+                         "mm_pair_first_clusters=0, mm_stream_max_ctas=64, mm_stream_lsu=0; repeatable")
     ap.add_argument("--ep-layer-steps", type=int, default=10,
                     help="N > 1, default workload: steps of the expert-parallel layer run after the headline (0 = skip)")
     args = ap.parse_args()
@@ -821,6 +829,12 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    if args.tunable:
+        from expert_specialization_moe_b200 import _cabi as _tun
+        for item in args.tunable:
+            name, _, value = item.partition("=")
+            _tun.set_tunable(name.strip(), int(value))
+        config["tunables"] = list(args.tunable)
     dist = None
     if world > 1:
         import torch.distributed as dist
