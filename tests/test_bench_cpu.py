@@ -53,3 +53,25 @@ def test_reference_arm_prints_contract_line():
     for key in ("metric", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "dtype", "data",
                 "config"):
         assert key in line
+
+
+def test_load_balanced_placement_replicates_the_hottest_expert_and_keeps_every_row():
+    counts = bench.zipf_counts(32768, 256, 1.2, 0)
+    for world in (2, 4, 8):
+        shards, note = bench.place_experts(counts, world, "load_balanced", 4096, 7168)
+        assert len(shards) == world and len({len(s) for s in shards}) == 1          # same number of expert slots
+        assert sum(int(s.sum()) for s in shards) == 32768                            # replicas split rows, none lost
+        rows = [int(s.sum()) for s in shards]
+        contiguous = [int(s.sum()) for s in bench.place_experts(counts, world, "contiguous", 4096, 7168)[0]]
+        assert max(rows) <= max(contiguous)
+        fair = 32768 // world
+        assert max(int(s.max()) for s in shards) <= max(fair, int(counts.max()) // 2 + 1)
+    shards8, note8 = bench.place_experts(counts, 8, "load_balanced", 4096, 7168)
+    assert "1 expert(s)" in note8 and max(int(s.sum()) for s in shards8) < 5000       # 11822 rows under contiguous
+
+
+def test_reference_benchmark_row_distribution():
+    c = bench.ref_dist_counts(4096, seed=3)
+    assert c.min() >= 1 and c.max() <= 1024
+    share = [(c <= 32).mean(), ((c >= 32) & (c <= 64)).mean(), ((c >= 64) & (c <= 128)).mean(), (c >= 128).mean()]
+    assert abs(share[0] - 0.70) < 0.03 and abs(share[3] - 0.05) < 0.015
