@@ -309,6 +309,26 @@ class CpuReferenceSample:
                 f"torch.mm per expert")
 
 
+def oracle_spot_check(wl, counts, N, K):
+    """Part of the cpu_baseline leg: the CPU path (oracle dequantise + fp32 matmul) on the DEVICE's own operands for
+    one small expert and one 128-column tile, against what the GPU wrote there — so the two arms of this benchmark
+    are seen to compute the same thing, not only to be timed on the same shapes."""
+    from oracle import grouped_gemm_oracle as G
+    from oracle import mxfp8_quant_oracle as Q
+    nz = [e for e in range(len(counts)) if counts[e] > 0]
+    e = min(nz, key=lambda i: (abs(int(counts[i]) - 24), i))          # an expert of about two dozen rows
+    m, off, bo, kb = int(counts[e]), int(wl["eo_h"][e]), int(wl["bo_h"][e]), K // 32
+    a = wl["a"].view(torch.uint8)[off:off + m].cpu()
+    sa = wl["sfa"].reshape(-1)[(torch.from_numpy(Q.sf_swizzled_offsets(m, K)) + bo * kb).to(wl["sfa"].device)].cpu()
+    w = wl["w"].view(torch.uint8)[e, :128].cpu()
+    sb = wl["sfb"].reshape(-1)[(torch.from_numpy(Q.sf_swizzled_offsets(N, K))[:128] + e * N * kb).to(wl["sfb"].device)].cpu()
+    ref = torch.mm(G.dequant_mxfp8(a, sa), G.dequant_mxfp8(w, sb).t())
+    got = wl["d"][off:off + m, :128].float().cpu()
+    rel, cos = G.rel_err_and_cosine(got, ref)
+    return {"expert": int(e), "rows": m, "columns": "0..127", "rel_err": rel, "cosine": cos,
+            "ok": bool(rel <= 1e-2 and cos >= 0.9999)}
+
+
 def cpu_reference_rate(counts, N, K, seed, budget_s=20.0, threads=None):
     """One timed pass over a sample sized for about `budget_s` seconds (assuming ~0.2 TFLOP/s of host throughput)."""
     sample = CpuReferenceSample(counts, N, K, seed, max_flops=budget_s * 0.2e12)
@@ -345,7 +365,9 @@ def bench_ep_layer(args, device, rank, world, dist):
             fx = ep.PipelinedExchange(E, topk, tokens, H, device, capacity_rows=2 * tokens * topk)
         else:
             fx = ep.FusedExchange(E, topk, tokens, H, device, capacity_rows=2 * tokens * topk)
-        step = lambda: fx.forward(x, ids, wts, shard)
+        out_buf = None if args.workload == "qwen3_ep_pipelined" else torch.empty_like(x)
+        step = (lambda: fx.forward(x, ids, wts, shard)) if out_buf is None else \
+               (lambda: fx.forward(x, ids, wts, shard, out=out_buf))
     else:
         step = lambda: ep.moe_forward(x, ids, wts, E, shard.forward)
 
@@ -948,6 +970,8 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             r, cores, sdesc = cpu_reference_rate(counts_all, N, K, seed=100, budget_s=args.cpu_budget)
             line["cpu_baseline"] = {"value": r, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sdesc}
+            if ref is None:
+                line["cpu_baseline"]["gpu_result_check"] = oracle_spot_check(wl, counts, N, K)
     del wl
     torch.cuda.empty_cache()
     # N > 1, default workload: the expert-parallel layer (dispatch / combine over peer memory) rides along, outside the

@@ -201,12 +201,16 @@ class ExpertShard:
         cap, dev = a.shape[0], a.device
         if work.get("cap") != cap:
             work.clear()
+            ps = lambda n, k: torch.tensor([[0, n, k]] * self.e_local, dtype=torch.int32, device=dev)
             work.update(cap=cap,
                         h1=torch.empty((cap, self.n1), dtype=torch.bfloat16, device=dev),
                         a2=torch.empty((cap, self.i), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn),
-                        sfa2=torch.zeros((sfa.shape[0], self.i // 32), dtype=torch.uint8, device=dev))
-        ps1 = torch.stack([rows, torch.full_like(rows, self.n1), torch.full_like(rows, self.h)], dim=1).contiguous()
-        ps2 = torch.stack([rows, torch.full_like(rows, self.h), torch.full_like(rows, self.i)], dim=1).contiguous()
+                        sfa2=torch.zeros((sfa.shape[0], self.i // 32), dtype=torch.uint8, device=dev),
+                        ps1=ps(self.n1, self.h), ps2=ps(self.h, self.i))
+        # problem lists live in the work set: only the row counts change from step to step (no allocation per step)
+        ps1, ps2 = work["ps1"], work["ps2"]
+        ps1[:, 0].copy_(rows)
+        ps2[:, 0].copy_(rows)
         mm(work["h1"], a, self.w1.transpose(1, 2), sfa, self.sf1, ps1, eo, bo)
         silu_mul_quant(work["h1"], ps2, eo, bo, work["a2"], work["sfa2"])
         if scatter is None:
@@ -350,28 +354,32 @@ class FusedExchange:
                                                      self.capacity, self.scale_bytes, s))
         return self.codes, self.scales
 
-    def combine(self, y: torch.Tensor, plan: dict, topk_weights: torch.Tensor) -> torch.Tensor:
+    def combine(self, y: torch.Tensor, plan: dict, topk_weights: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """y [capacity, H] expert outputs in receive order -> [tokens, H] = sum_j w[token, j] * y(token, j)."""
         assert y.shape == (self.capacity, self.hidden) and y.dtype == self.dtype and y.is_contiguous()
         s = torch.cuda.current_stream(y.device).cuda_stream
         self._check(self._lib.es_b200_ep_combine_push(
             y.data_ptr(), self.meta.data_ptr(), plan["total_rows"].data_ptr(), self._peer_pairs, self.world,
             self.capacity, self.tokens * self.topk, self.hidden, 2, s))
-        return self.reduce(topk_weights)
+        return self.reduce(topk_weights, out)
 
-    def reduce(self, topk_weights: torch.Tensor) -> torch.Tensor:
-        """After every rank's expert outputs have arrived in my (token, j) slots: out[t] = sum_j w[t, j] * slot(t, j)."""
+    def reduce(self, topk_weights: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """After every rank's expert outputs have arrived in my (token, j) slots: out[t] = sum_j w[t, j] * slot(t, j).
+        `out`: caller's [tokens, H] result buffer (a serving loop passes the same one every step: no allocation)."""
         dev = self.pairs.device
         self.barrier(dev)
-        out = torch.empty((self.tokens, self.hidden), dtype=self.dtype, device=dev)
-        w = topk_weights.to(torch.float32).contiguous()
+        if out is None:
+            out = torch.empty((self.tokens, self.hidden), dtype=self.dtype, device=dev)
+        w = topk_weights if (topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()) \
+            else topk_weights.to(torch.float32).contiguous()
         self._check(self._lib.es_b200_ep_topk_weighted_sum(self.pairs.data_ptr(), self._dtype_code, w.data_ptr(),
                                                            out.data_ptr(), self.tokens, self.topk, self.hidden,
                                                            torch.cuda.current_stream(dev).cuda_stream))
         return out
 
     def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, shard: ExpertShard,
-                fuse_combine: bool = True) -> torch.Tensor:
+                fuse_combine: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One MoE layer.  With fuse_combine the down GEMM's epilogue stores each output row straight into the
         sender's slot; otherwise the rows go through a dense output and es_b200_ep_combine_push."""
         assert self.dtype == torch.bfloat16 or not fuse_combine
@@ -381,8 +389,8 @@ class FusedExchange:
         y = shard.forward_codes(a, sfa, plan["rows"], plan["expert_offsets"], plan["blockscale_offsets"], self.work,
                                 scatter)
         if fuse_combine:
-            return self.reduce(topk_weights)
-        return self.combine(y, plan, topk_weights)
+            return self.reduce(topk_weights, out)
+        return self.combine(y, plan, topk_weights, out)
 
 
 class PipelinedExchange:
