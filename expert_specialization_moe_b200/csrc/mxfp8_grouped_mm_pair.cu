@@ -109,14 +109,23 @@ struct TileInfo {
 };
 
 __device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
-                                                const int* expert_offsets) {
+                                                const int* expert_offsets, int n, int n_pairs) {
   TileInfo ti;
   ti.e = upper_bound_expert(prefix, num_experts, t);
   const int i = t - prefix[ti.e];
   const int m = problem_sizes[ti.e * 3];
   const int token_tiles = (m + TOK_TILE - 1) / TOK_TILE;
-  ti.np = i / token_tiles;
-  ti.tt = i - ti.np * token_tiles;     // token tile runs fastest: concurrent pairs share the weight slab in L2
+  // Consecutive items run at the same time on different CTA pairs and share one operand in L2 while they sweep the
+  // other: the swept operand should be the SMALLER one.  Token tile fastest (items share a weight slab and sweep the
+  // expert's m x k tokens) unless the expert has more token rows than weight rows; then weight pair fastest (items
+  // share a token tile and sweep the n x k weights).
+  if (m <= n) {
+    ti.np = i / token_tiles;
+    ti.tt = i - ti.np * token_tiles;
+  } else {
+    ti.tt = i / n_pairs;
+    ti.np = i - ti.tt * n_pairs;
+  }
   const int r_local = ti.tt * TOK_TILE;
   const int rem = m - r_local;
   ti.valid = rem < TOK_TILE ? rem : TOK_TILE;
@@ -270,7 +279,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         break;
       }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
       const int half0 = ti.n0 >> 1, half1 = ti.n1 >> 1;     // token rows of each sub-tile held by each CTA
       const int xi0 = box_index(half0), xi1 = box_index(half1);
       const uint32_t tx = 2u * (W_BYTES + box_rows_of(xi0) * TILE_K + (ti.n1 ? box_rows_of(xi1) * TILE_K : 0u) +
@@ -333,7 +342,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         ptx::mbar_arrive(&ctl->q_empty[qs]);
         if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
         const uint32_t n_mma = sub == 0 ? ti.n0 : ti.n1;
         const uint32_t d_acc = tmem_base + sub * ACC_COLS;
         for (int kt = 0; ok && kt < kt_count; ++kt) {
@@ -384,7 +393,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         ptx::mbar_arrive(&ctl->q_empty[qs]);
         if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
         for (int kt = 0; kt < kt_count; ++kt) {
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
@@ -427,7 +436,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       if (lane == 0) ptx::mbar_arrive_cluster(&ctl->q_empty[qs], 0);   // leader's barrier
       if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
       if (sub == 1 && ti.n1 == 0) continue;               // an item of <= 192 rows does not use accumulator 1
       const int nt = ti.np * 2 + (int)rank;
       const bool store = nt < n_tiles;
