@@ -48,6 +48,30 @@ def test_static_scratch_route_count_matches_the_scratch_version_twice():
         assert torch.equal(res["static"][1][0], want)
 
 
+def test_static_scratch_route_count_allocates_no_device_memory():
+    """The point of the entry point: a call takes no device memory from anybody.  The driver's free-memory figure is
+    the same before and after a call (the first call on the device, which looks up the static array's address, was
+    made by the test above or is made here before the measurement)."""
+    from expert_specialization_moe_b200 import _cabi
+    lib = _cabi.load()
+    dev = torch.device("cuda", 0)
+    ids = torch.randint(0, 64, (512, 4), device=dev, dtype=torch.int64)
+    base = torch.empty((256, 64), dtype=torch.int32, device=dev)
+    counts = torch.empty((1, 64), dtype=torch.int32, device=dev)
+    table = (ctypes.c_void_p * 1)(counts.data_ptr())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    call = lambda: lib.es_b200_ep_route_count_static(ids.data_ptr(), 1, ids.numel(), 64, base.data_ptr(), table, 0, 1, stream)
+    assert call() == 0
+    torch.cuda.synchronize(dev)
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    for _ in range(3):
+        assert call() == 0
+    torch.cuda.synchronize(dev)
+    free_after, _ = torch.cuda.mem_get_info(dev)
+    assert free_after == free_before
+    assert torch.equal(counts[0].cpu(), torch.bincount(ids.reshape(-1).cpu(), minlength=64).to(torch.int32))
+
+
 def test_static_scratch_route_count_rejects_more_experts_than_it_holds():
     from expert_specialization_moe_b200 import _cabi
     lib = _cabi.load()
