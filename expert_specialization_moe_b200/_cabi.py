@@ -70,6 +70,8 @@ def _declare(lib):
     lib.es_b200_ep_route_tables.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_int64, c_void_p]
+    lib.es_b200_error_epoch.restype = ctypes.c_uint64
+    lib.es_b200_error_epoch.argtypes = []
     lib.es_b200_set_tunable.restype = c_int
     lib.es_b200_set_tunable.argtypes = [c_char_p, c_int]
     lib.es_b200_check_status.restype = c_int
@@ -135,14 +137,22 @@ def grouped_mm_scratch(device, stream_ptr: int):
     zeroed by every call, so one buffer per stream serves every call on that stream (graph replays included)."""
     import torch
     key = (device.index, stream_ptr)
-    buf = _SCRATCH.get(key)
-    if buf is None:
-        nbytes = int(load().es_b200_grouped_mm_scratch_bytes(0, 0, 0, 0))
+    lib = load()
+    epoch = int(lib.es_b200_error_epoch())
+    entry = _SCRATCH.get(key)
+    if entry is None or entry[1] != epoch:
+        # first use, or a device-side error was reported since the buffer was last zeroed: (re-)zero it on the stream
         with torch.cuda.stream(torch.cuda.ExternalStream(stream_ptr, device=device) if stream_ptr else
                                torch.cuda.default_stream(device)):
-            buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
-        _SCRATCH[key] = buf
-    return buf
+            if entry is None:
+                nbytes = int(lib.es_b200_grouped_mm_scratch_bytes(0, 0, 0, 0))
+                buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            else:
+                buf = entry[0]
+                buf.zero_()
+        entry = (buf, epoch)
+        _SCRATCH[key] = entry
+    return entry[0]
 
 
 def set_tunable(name: str, value: int):

@@ -1,4 +1,5 @@
 // Library-level entry points of the es_b200 C ABI: version, error strings, per-device property cache.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -44,6 +45,12 @@ int get_device_info(DeviceInfo* out) {
   return ES_B200_OK;
 }
 
+// Counts the device-side errors that es_b200_check_status has reported.  A kernel that gave up may have left the work
+// counters of the call's scratch non-zero; whoever owns a scratch buffer compares this number with the one it saw when
+// it last zeroed the buffer and zeroes it again when it has moved.
+static std::atomic<uint64_t> g_error_epoch{0};
+void note_device_error() { g_error_epoch.fetch_add(1, std::memory_order_relaxed); }
+
 static int env_or(const char* name, int fallback) {
   const char* v = getenv(name);
   return v ? atoi(v) : fallback;
@@ -78,6 +85,8 @@ extern "C" int es_b200_set_tunable(const char* name, int value) {
     }
   return fail(ES_B200_ERR_INVALID_ARGUMENT, "unknown tunable '%s'", name);
 }
+
+extern "C" uint64_t es_b200_error_epoch(void) { return es_b200::g_error_epoch.load(std::memory_order_relaxed); }
 
 extern "C" const char* es_b200_version(void) { return "es_b200 0.2 (sm_100a)"; }
 

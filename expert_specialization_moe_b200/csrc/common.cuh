@@ -63,6 +63,7 @@ struct Tunables {
   int mm_stream_lsu;            // 1: the streaming kernels fill every other ring slot with cp.async instead of TMA
 };
 Tunables& tunables();
+void note_device_error();   // es_b200_check_status found status bits set (see es_b200_error_epoch)
 
 // ---- device: programmatic dependent launch ---------------------------------------------------
 // Both are no-ops when the kernel was not launched with the programmatic-stream-serialization attribute.

@@ -715,6 +715,7 @@ extern "C" int es_b200_check_status(void* stream, uint32_t* raw_status) {
   if (rc2 != ES_B200_OK) return rc2;
   v |= v2;
   if (raw_status) *raw_status = v;
+  if (v != 0) note_device_error();
   if (v != 0)
     return fail(ES_B200_ERR_DEVICE_TIMEOUT,
                 "a bounded device-side wait gave up or an index was out of range (status bits 0x%x)", v);

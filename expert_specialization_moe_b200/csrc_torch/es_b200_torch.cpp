@@ -31,18 +31,27 @@ void check_rc(int rc) {
   TORCH_CHECK(false, (msg && msg[0]) ? msg : es_b200_strerror(rc));
 }
 
-// Work-counter scratch of the grouped GEMM, one per (device, stream): zeroed when created, left zeroed by every call.
+// Work-counter scratch of the grouped GEMM, one per (device, stream): zeroed when created, left zeroed by every call,
+// and zeroed again (on the stream, before the call) when a device-side error has been reported since.
+struct Scratch {
+  at::Tensor buf;
+  uint64_t epoch;
+};
 at::Tensor& mm_scratch(const at::Tensor& like, cudaStream_t stream) {
   static std::mutex mu;
-  static std::unordered_map<uint64_t, at::Tensor> cache;
+  static std::unordered_map<uint64_t, Scratch> cache;
   const uint64_t key = (reinterpret_cast<uint64_t>(stream) << 8) ^ static_cast<uint64_t>(like.get_device() + 1);
+  const uint64_t epoch = es_b200_error_epoch();
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it == cache.end()) {
     const int64_t n = static_cast<int64_t>(es_b200_grouped_mm_scratch_bytes(0, 0, 0, 0));
-    it = cache.emplace(key, at::zeros({n}, like.options().dtype(at::kByte))).first;   // enqueued on the current stream
+    it = cache.emplace(key, Scratch{at::zeros({n}, like.options().dtype(at::kByte)), epoch}).first;   // on the current stream
+  } else if (it->second.epoch != epoch) {
+    it->second.buf.zero_();
+    it->second.epoch = epoch;
   }
-  return it->second;
+  return it->second.buf;
 }
 
 void check_problem_tensors(const at::Tensor& problem_sizes, const at::Tensor& expert_offsets) {

@@ -85,11 +85,14 @@ int es_b200_mxfp8_silu_mul_grouped_quant(const void* gate_up, int input_dtype, c
  *   - zero it once (cudaMemset) before the first call that uses it; every call leaves it zeroed, so the same buffer
  *     serves any number of calls on one stream, graph replays included;
  *   - calls that may overlap on the GPU (different streams) need different scratch buffers;
- *   - after es_b200_check_status has reported a device-side error, zero it again.
+ *   - after es_b200_check_status has reported a device-side error, zero it again (a kernel that gave up may have
+ *     left counters behind); es_b200_error_epoch() counts those reports, so an owner of scratch buffers can compare
+ *     it with the value it saw when it last zeroed a buffer.
  * scratch may be NULL: the kernels then deal their tiles round-robin and a large call runs its row-count buckets one
  * after the other instead of side by side (slower, same results).
  */
 size_t es_b200_grouped_mm_scratch_bytes(int num_experts, int64_t num_rows, int n, int k);
+uint64_t es_b200_error_epoch(void);
 
 /*
  * MXFP8 block-scaled grouped GEMM:  d[off_e + i, :] = sum_k a[off_e + i, k] 2^(sfa-127) * b[e, :, k] 2^(sfb-127)

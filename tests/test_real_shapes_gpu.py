@@ -242,11 +242,15 @@ def test_misaligned_blockscale_offset_is_reported_and_skipped():
     rc, raw = C.device_status()
     assert rc == 0
     assert list(inp["bo"]) == [0, 128, 384]
+    from expert_specialization_moe_b200 import _cabi
+    epoch = int(_cabi.load().es_b200_error_epoch())
     bad = dict(inp, bo=np.array([0, 192, 384], dtype=np.int32))       # expert 1: 64 rows off an atom
     d = C.run_mxfp8_mm_op(bad, fill=5.0)
     rc, raw = C.device_status()
     assert rc != 0 and (raw & 0x80)
+    assert int(_cabi.load().es_b200_error_epoch()) == epoch + 1       # owners of scratch buffers re-zero them on this
     assert torch.equal(d[:40], good[:40]) and torch.equal(d[240:], good[240:])
     assert bool((d[40:240] == 5.0).all())
     rc, raw = C.device_status()
     assert rc == 0
+    assert torch.equal(C.run_mxfp8_mm_op(inp, fill=5.0), good)         # the next call is unaffected
