@@ -75,50 +75,14 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], int c, int 
   }
 }
 
-// Drains `n_cols` accumulator columns (a multiple of 16) starting at TMEM address `taddr` (this warp's lane quadrant)
-// and stores the first `valid` of them: column j goes to dst[j * ld + 0..31] (dst = &d[first token][first n of warp]).
-// `release` is called once, right after the last TMEM read has completed (the accumulator may then be overwritten).
-// TOK = tokens per pass through the shared-memory tile (32: 2 KB per warp; 16: 1 KB; 8: 512 bytes).
-// With a scatter map, column j goes to the mapped row of output row `first_row + j`, at column offset `col_off`
-// (`dst` is then unused); `status` is the kernel's error word.
-template <typename OutT, int TOK = 32, class Release>
-__device__ __forceinline__ void drain_accumulator(uint32_t taddr, int n_cols, int valid, OutT* stage_warp, OutT* dst,
-                                                  int64_t ld, bool do_store, int lane, Release release,
-                                                  const RowScatter& scatter, int64_t first_row, int col_off,
-                                                  uint32_t* status) {
-  // two register sets: the TMEM read of chunk c+1 is in flight while chunk c goes through shared memory
-  uint32_t va[32], vb[32];
-  ptx::tc_ld_32x32b_x32(taddr, va);
-  for (int c0 = 0; c0 < n_cols; c0 += 64) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int c = c0 + h * 32;
-      if (c >= n_cols) break;
-      // scatter map: lane l fetches the destination of token c + l now, so that the load's latency hides behind the
-      // TMEM read and the conversions; the store loop picks it up with a shuffle
-      OutT* dest = nullptr;
-      if (scatter.meta != nullptr && do_store)
-        dest = scatter_row_ptr<OutT>(scatter, first_row + c + lane, c + lane < valid, ld, col_off, status);
-      ptx::tc_wait_ld();                                    // chunk c is in registers (va if h == 0, vb otherwise)
-      const bool more = c + 32 < n_cols;
-      if (more) {
-        if (h == 0) ptx::tc_ld_32x32b_x32(taddr + c + 32, vb); else ptx::tc_ld_32x32b_x32(taddr + c + 32, va);
-      } else {
-        release();
-      }
-      if (do_store) {
-        if (h == 0) store_chunk<OutT, TOK>(va, c, valid, stage_warp, dst, ld, lane, scatter, dest);
-        else store_chunk<OutT, TOK>(vb, c, valid, stage_warp, dst, ld, lane, scatter, dest);
-      }
-    }
-  }
-}
-
 // Accumulator kept as PARTS partial sums (column blocks `part_stride` columns apart): several threads issue the MMAs
 // of a tile, each into a block of its own, and the sum is taken here in fp32, in block order.  `parts_written` (1 ..
 // PARTS) blocks hold data (a tile with fewer K steps than issuing threads leaves the others untouched).  Drains
-// `n_cols` columns (a multiple of 16, at most 128) and stores the first `valid` of them like drain_accumulator;
-// `release` is called once, after the last TMEM read.
+// `n_cols` columns (a multiple of 16, at most 128) starting at TMEM address `taddr` (this warp's lane quadrant) and
+// stores the first `valid` of them: column j goes to dst[j * ld + 0..31] (dst = &d[first token][first n of warp]); with
+// a scatter map, to the mapped row of output row `first_row + j` at column offset `col_off` (`dst` is then unused).
+// `release` is called once, after the last TMEM read (the accumulator may then be overwritten); `status` is the
+// kernel's error word.
 template <typename OutT, int PARTS, class Release>
 __device__ __forceinline__ void drain_partial_sums(uint32_t taddr, uint32_t part_stride, int parts_written, int n_cols,
                                                    int valid, OutT* stage_warp, OutT* dst, int64_t ld, int lane,
@@ -156,28 +120,79 @@ __device__ __forceinline__ void drain_partial_sums(uint32_t taddr, uint32_t part
   }
 }
 
-// The same for a warp that shares its lane quadrant with other warps: it takes the 32-column chunks first_chunk,
-// first_chunk + chunk_stride, ... and keeps one register set — the warps of a quadrant hide each other's TMEM
-// latency.  A warp without a chunk only calls `release`.
-template <typename OutT, int TOK, class Release>
-__device__ __forceinline__ void drain_accumulator_shared(uint32_t taddr, int n_cols, int valid, OutT* stage_warp,
-                                                         OutT* dst, int64_t ld, bool do_store, int lane,
-                                                         Release release, const RowScatter& scatter,
-                                                         int64_t first_row, int col_off, uint32_t* status,
-                                                         int first_chunk, int chunk_stride) {
-  if (first_chunk >= n_cols) {
-    release();
-    return;
-  }
-  uint32_t v[32];
-  for (int c = first_chunk; c < n_cols; c += chunk_stride) {
-    OutT* dest = nullptr;
-    if (scatter.meta != nullptr && do_store)
-      dest = scatter_row_ptr<OutT>(scatter, first_row + c + lane, c + lane < valid, ld, col_off, status);
-    ptx::tc_ld_32x32b_x32(taddr + c, v);
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_pair_from_f32(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack_pair_from_f32<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair_from_f32<__half>(float lo, float hi) {
+  const __half2 p = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&p);
+}
+
+// ---- an epilogue that holds converted chunks in registers (the CTA-pair kernel) ---------------------------------
+// A held chunk is 32 accumulator columns (tokens) of the warp's 32 lanes (n): register i = tokens (2i, 2i+1) as two
+// 16-bit values.  The warp reads all its chunks of an accumulator into held registers, hands the accumulator back to
+// the MMA lanes, and stores afterwards: the stores of an item take several thousand cycles while the K loop's operand
+// traffic shares the memory system, and the next item's MMAs run meanwhile.
+
+// TMEM -> held registers (the caller releases the accumulator after its last read_held_chunk)
+template <typename OutT>
+__device__ __forceinline__ void read_held_chunk(uint32_t taddr, uint32_t (&held)[16]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint32_t v[16];
+    ptx::tc_ld_32x32b_x16(taddr + h * 16, v);
     ptx::tc_wait_ld();
-    if (c + chunk_stride >= n_cols) release();
-    if (do_store) store_chunk<OutT, TOK>(v, c, valid, stage_warp, dst, ld, lane, scatter, dest);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      held[h * 8 + i] = pack_pair_from_f32<OutT>(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+  }
+}
+
+// Dense output without shared memory: a warp-wide 2-byte store writes the 64 contiguous bytes of one token row (two
+// full sectors).  The CTA-pair kernel's K loop keeps the shared-memory pipe busy (operand reads of the MMAs plus the
+// TMA fills come to ~120 of the 128 bytes per cycle) and every store -> sync -> load round trip of a staged epilogue
+// queues behind that traffic (measured: ~2900 cycles per 32 x 32 chunk staged, ~2500 direct with 8x the stores).
+// `out` = &d[first token of the chunk][first n of the warp]; `rows` = token rows of the chunk that exist (may be
+// <= 0 or > 32).
+__device__ __forceinline__ void store_held_chunk_dense(const uint32_t (&held)[16], uint16_t* out, int64_t ld, int rows,
+                                                       int lane) {
+  out += lane;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (2 * i < rows) out[0] = (uint16_t)(held[i] & 0xFFFFu);
+    if (2 * i + 1 < rows) out[ld] = (uint16_t)(held[i] >> 16);
+    out += 2 * ld;
+  }
+}
+
+// Scattered output: through the warp's 512-byte shared-memory tile, 8 tokens per pass, so that ONE shuffle per pass
+// hands every lane the destination row it stores 16 bytes of; a shuffle per token row (what the direct form would
+// need) costs more than the staging — shuffles share the pipe that the K loop keeps busy.  `dest_row`: lane l holds
+// the destination of token l of the chunk (null = skip).
+template <typename OutT>
+__device__ __forceinline__ void store_held_chunk_scatter(const uint32_t (&held)[16], OutT* stage_warp, OutT* dest_row,
+                                                         int lane) {
+  const int part = lane & 3;
+  const int tok = lane >> 2;
+  uint16_t* stage16 = reinterpret_cast<uint16_t*>(stage_warp);
+  const unsigned long long bits = reinterpret_cast<unsigned long long>(dest_row);
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      stage16[(2 * j) * 32 + lane] = (uint16_t)(held[p * 4 + j] & 0xFFFFu);
+      stage16[(2 * j + 1) * 32 + lane] = (uint16_t)(held[p * 4 + j] >> 16);
+    }
+    __syncwarp();
+    const uint4 val = *reinterpret_cast<const uint4*>(stage16 + tok * 32 + part * 8);
+    OutT* out = reinterpret_cast<OutT*>(__shfl_sync(0xffffffffu, bits, p * 8 + tok));
+    if (out != nullptr) *reinterpret_cast<uint4*>(out + part * 8) = val;
+    __syncwarp();
   }
 }
 

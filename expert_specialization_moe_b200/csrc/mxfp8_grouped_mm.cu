@@ -72,11 +72,15 @@ constexpr uint32_t SF_SLOT_COLS = 8;    // per ring slot: 4 columns of weight sc
 
 // A streaming shape: experts with at most TOK_TILE rows (ONE token tile per expert: the tile's token scales are then
 // exactly one 128-row atom), STAGES ring slots, LANES MMA-issuing threads = partial accumulators.
-template <int TOK_TILE_, int STAGES_, int LANES_>
+template <int TOK_TILE_, int STAGES_, int LANES_, bool SECOND_LOAD_PATH_>
 struct Shape {
   static constexpr int TOK_TILE = TOK_TILE_;     // token rows per tile (tcgen05.mma N, runtime multiple of 16)
   static constexpr int STAGES = STAGES_;
   static constexpr int LANES = LANES_;
+  // odd ring slots by cp.async: pays where the slot is mostly weights (measured per SM on 64 CTAs: 66 vs 49 GB/s for
+  // the 32-token shape); with a 14 KB token tile per slot the 128 loader threads copy as many token bytes (L2 hits)
+  // as weight bytes and the shape is slower with it (48 vs 52 GB/s)
+  static constexpr bool SECOND_LOAD_PATH = SECOND_LOAD_PATH_;
   static constexpr int X_BYTES = TOK_TILE * TILE_K;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // W | X | weight scales | token scales
   static constexpr uint32_t ACC_COLS = LANES * TOK_TILE;                 // one accumulator buffer: LANES partials
@@ -85,8 +89,8 @@ struct Shape {
   static_assert(TOK_TILE % 16 == 0 && TOK_TILE <= 128 && (LANES == 1 || LANES == 2 || LANES == 4), "tile shape");
   static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 };
-using ShapeTiny = Shape<32, 10, 4>;   // 21 KB slots; TMEM: 2 x 4 x 32 accumulator columns + 80 scale columns
-using ShapeMid = Shape<112, 6, 2>;    // 31 KB slots; TMEM: 2 x 2 x 112 accumulator columns + 48 scale columns
+using ShapeTiny = Shape<32, 10, 4, true>;   // 21 KB slots; TMEM: 2 x 4 x 32 accumulator columns + 80 scale columns
+using ShapeMid = Shape<112, 6, 2, false>;   // 31 KB slots; TMEM: 2 x 2 x 112 accumulator columns + 48 scale columns
 
 constexpr uint32_t ERR_PRODUCER = 1u, ERR_MMA = 2u, ERR_EPILOGUE = 4u, ERR_SCALE_COPY = 8u, ERR_LOADER = 0x400u;
 constexpr int QUEUE_DEPTH = 4;          // tile indices in flight between the producer lane and the other roles
@@ -533,7 +537,7 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const int use_lsu = tunables().mm_stream_lsu ? 1 : 0;
+  const int use_lsu = (S::SECOND_LOAD_PATH && tunables().mm_stream_lsu) ? 1 : 0;
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], map_sfx, map_sfw,
                                  static_cast<const uint8_t*>(c.a), static_cast<const uint8_t*>(c.b), c.sfa, c.sfb,
                                  (int)c.num_rows, (long long)(c.sfa_rows * (c.k / 32)), use_lsu,

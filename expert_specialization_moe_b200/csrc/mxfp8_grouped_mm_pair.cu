@@ -12,13 +12,12 @@
 // columns, and the second sub-tile starts on a 64-row boundary of the 128-row scale atoms, which a TMEM column
 // offset addresses.
 //
-//   warp 0    producer (both CTAs): per K step lanes 0..6 each issue one TMA load (own weight rows, own halves of
+//   warp 0    producer (both CTAs): per K step lanes 0..4 each issue one TMA load (own weight rows, own halves of
 //             the two token sub-tiles, own weight scale atom, the item's token scale atoms); all completion bytes
 //             are credited to the leader CTA's barrier
 //   warp 1    TMEM allocation (both CTAs); in the leader CTA one lane issues sub-tile 0's four tcgen05.mma per K step
-//   warps 2-9   epilogue of accumulator 0 (both CTAs): own 128 accumulator lanes -> bf16/fp16 -> global; two warps
-//               per TMEM lane quadrant take alternate 32-column chunks
-//   warps 10-17 epilogue of accumulator 1, at the same time
+//   warps 2-17  epilogue (both CTAs): own 128 accumulator lanes -> registers (bf16/fp16) -> accumulators handed back
+//               -> global; four warps per TMEM lane quadrant share the 32-column chunks of both accumulators
 //   warp 18     leader CTA, one lane: sub-tile 1's four tcgen05.mma per K step
 //   warp 19     leader CTA, one lane: the K step's four tcgen05.cp (scales smem -> TMEM of both CTAs)
 //
@@ -67,9 +66,8 @@ static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 
 constexpr uint32_t ERR_PRODUCER = 0x10u, ERR_MMA = 0x20u, ERR_EPILOGUE = 0x40u;
 constexpr uint32_t ERR_SCALE_COPY = 0x100u;
-constexpr int EPI_WARPS = 16;                              // per accumulator: 4 lane quadrants x 2 warps
-constexpr int EPI_TOK = 8;                                 // tokens per pass of an epilogue warp's shared-memory tile
-constexpr int EPI_BYTES_PER_WARP = EPI_TOK * 32 * 2;       // 512 bytes
+constexpr int EPI_WARPS = 16;                              // 4 TMEM lane quadrants x 4 warps
+constexpr int EPI_BYTES_PER_WARP = 8 * 32 * 2;             // 512 bytes: 8 tokens x 32 n (scattered output only)
 constexpr int MMA_B_WARP = 2 + EPI_WARPS;                  // 18
 constexpr int COPY_WARP = MMA_B_WARP + 1;                  // 19
 constexpr int QUEUE_DEPTH = 4;
@@ -82,15 +80,36 @@ struct SharedCtl {
   uint64_t empty[STAGES];       // 2 arrivals: one commit from each MMA lane
   uint64_t sf_ready[STAGES];    // leader only: the stage's scales are in the TMEM of both CTAs
   uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];       // used in the leader CTA only (16 arrivals: 8 epilogue warps x 2 CTAs)
+  uint64_t tmem_empty[2];       // used in the leader CTA only (32 arrivals: 16 epilogue warps x 2 CTAs)
                                 // index = accumulator (sub-tile 0 / 1)
-  uint64_t q_full[QUEUE_DEPTH];   // 1 arrival (from the leader's producer lane, in both CTAs): q_tile[slot] is written
+  uint64_t q_full[QUEUE_DEPTH];   // 1 arrival from the leader's producer lane (in the partner CTA also the 8 bytes of
+                                  // the entry, sent with the arrival): q_item[slot] is written
   uint64_t q_empty[QUEUE_DEPTH];  // leader only: Q_CONSUMERS arrivals, every consuming role of both CTAs has read it
-  int q_tile[QUEUE_DEPTH];        // work item index, or -1: no more work
+  int2 q_item[QUEUE_DEPTH];       // x: work item index, or -1: no more work; y: the item's expert (found once, by
+                                  // the leader's producer lane)
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
-  int tile_prefix[ES_B200_MAX_EXPERTS + 1];
+  // [0, E]: exclusive prefix of the experts' item counts; behind it, as far as the array reaches (all experts when
+  // E <= 256), three tables of the first `cached` experts: token rows, first row, first scale row
+  int table[ES_B200_MAX_EXPERTS + 1];
+};
+
+// Per-expert facts that every role needs for every work item.  Reading them from global memory cost each role
+// ~2000 cycles per item (dependent L2 round trips behind a binary search), which the MMA lanes cannot hide: with
+// K = 768 an item is only ~5000 cycles of tensor work.  They are copied to shared memory once per CTA.
+struct ExpertTable {
+  const int* prefix;
+  const int* rows;         // shared-memory copies for experts below `cached`
+  const int* first_row;
+  const int* scale_row0;
+  int cached;
+  const int* problem_sizes;     // global memory, for experts at or above `cached`
+  const int* expert_offsets;
+  const int* blockscale_offsets;
+  __device__ __forceinline__ int m(int e) const { return e < cached ? rows[e] : problem_sizes[e * 3]; }
+  __device__ __forceinline__ int row0(int e) const { return e < cached ? first_row[e] : expert_offsets[e]; }
+  __device__ __forceinline__ int scale0(int e) const { return e < cached ? scale_row0[e] : blockscale_offsets[e]; }
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + EPI_WARPS * EPI_BYTES_PER_WARP + sizeof(SharedCtl);
@@ -108,12 +127,11 @@ struct TileInfo {
   int n_atoms;     // 1..3 atoms cover the item's valid rows
 };
 
-__device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
-                                                const int* expert_offsets, int n, int n_pairs) {
+__device__ __forceinline__ TileInfo decode_tile(int t, int e, const ExpertTable& tab, int n, int n_pairs) {
   TileInfo ti;
-  ti.e = upper_bound_expert(prefix, num_experts, t);
-  const int i = t - prefix[ti.e];
-  const int m = problem_sizes[ti.e * 3];
+  ti.e = e;
+  const int i = t - tab.prefix[e];
+  const int m = tab.m(e);
   const int token_tiles = (m + TOK_TILE - 1) / TOK_TILE;
   // Consecutive items run at the same time on different CTA pairs and share one operand in L2 while they sweep the
   // other: the swept operand should be the SMALLER one.  Token tile fastest (items share a weight slab and sweep the
@@ -133,7 +151,7 @@ __device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int nu
   ti.v1 = ti.valid - ti.v0;
   ti.n0 = (ti.v0 + 15) & ~15;
   ti.n1 = (ti.v1 + 15) & ~15;
-  ti.row0 = expert_offsets[ti.e] + r_local;
+  ti.row0 = tab.row0(e) + r_local;
   ti.atom0 = r_local >> 7;
   ti.n_atoms = (ti.valid + 127) >> 7;
   return ti;
@@ -146,21 +164,14 @@ __device__ __forceinline__ uint32_t box_rows_of(int idx) {
   return idx == 0 ? 8u : idx == 1 ? 16u : idx == 2 ? 32u : idx == 3 ? 64u : 96u;
 }
 
-template <typename OutT>
-__device__ __forceinline__ OutT from_f32(float v);
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
-
 struct Maps {
   CUtensorMap w;        // weights  [E*N, K] bytes, box 128 rows x 128 B, 128-byte swizzle
   CUtensorMap x[5];     // tokens   [T, K]   bytes, boxes of 8 / 16 / 32 / 64 / 96 rows
   CUtensorMap sfw;      // weight scale atoms, 512-byte records
-  CUtensorMap sfx;      // token scale atoms, 512-byte records
+  CUtensorMap sfx;      // token scale atoms as [128-row block][K block] of 512-byte records; box = 3 row blocks
 };
 
-template <typename OutT>
+template <typename OutT, bool HOLD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict__ d,
                              const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
@@ -185,7 +196,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&ctl->tmem_full[a], 1);
-      ptx::mbar_init(&ctl->tmem_empty[a], EPI_WARPS);
+      ptx::mbar_init(&ctl->tmem_empty[a], 2 * EPI_WARPS);
     }
     for (int q = 0; q < QUEUE_DEPTH; ++q) {
       ptx::mbar_init(&ctl->q_full[q], 1);
@@ -213,7 +224,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   const int n_pairs = (n_tiles + 1) >> 1;
   // only experts with at least min_rows rows belong to this kernel (the single-CTA kernel takes the others)
   // (an expert whose scales do not start on a 128-row atom cannot be addressed: reported and skipped)
-  block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
+  block_exclusive_scan(num_experts, ctl->table, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
     if (!(m > 0 && m >= min_rows)) return 0;
     if ((blockscale_offsets[e] & 127) != 0) {
@@ -222,21 +233,41 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     }
     return ((m + TOK_TILE - 1) / TOK_TILE) * n_pairs;
   });
-  // barriers and TMEM of both CTAs must exist before either CTA signals the other
+  ExpertTable tab;
+  {
+    const int room = (ES_B200_MAX_EXPERTS + 1 - (num_experts + 1)) / 3;
+    tab.cached = num_experts < room ? num_experts : room;
+    int* rows = ctl->table + num_experts + 1;
+    int* first_row = rows + tab.cached;
+    int* scale_row0 = first_row + tab.cached;
+    for (int e = threadIdx.x; e < tab.cached; e += THREADS) {
+      rows[e] = problem_sizes[e * 3];
+      first_row[e] = expert_offsets[e];
+      scale_row0[e] = blockscale_offsets[e];
+    }
+    tab.prefix = ctl->table;
+    tab.rows = rows;
+    tab.first_row = first_row;
+    tab.scale_row0 = scale_row0;
+    tab.problem_sizes = problem_sizes;
+    tab.expert_offsets = expert_offsets;
+    tab.blockscale_offsets = blockscale_offsets;
+  }
+  // barriers, TMEM and tables of both CTAs must exist before either CTA signals the other
   ptx::tc_fence_before_sync();
   ptx::cluster_sync();
   ptx::tc_fence_after_sync();
   pdl_launch_dependents();
 
   const uint32_t tmem_base = ctl->tmem_base;
-  const int total_tiles = ctl->tile_prefix[num_experts];
+  const int total_tiles = tab.prefix[num_experts];
   const int kt_count = k / TILE_K;
   const int sfw_atoms_per_expert = n_tiles * kt_count;
   volatile int* abort_flag = &ctl->abort_flag;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (warp 0 of each CTA)
-    // The whole warp walks the work list; per K step lanes 0..6 each issue ONE of the stage's loads in the same
+    // The whole warp walks the work list; per K step lanes 0..4 each issue ONE of the stage's loads in the same
     // instruction (a TMA issue costs the issuing thread ~80 cycles, five in a row would be a third of a stage time).
     int s = 0, qs = 0;
     uint32_t ph = 0, qph = 0;
@@ -245,27 +276,29 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     if (rank == 0 && lane == 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : pair;
     while (true) {
       // the leader publishes the next item (or the end mark) to both CTAs; the partner's producer reads its copy
-      int t = -1;
+      int t = -1, e = 0;
       bool q_ok = true;
       if (rank == 0) {
         if (lane == 0) {
           q_ok = ptx::mbar_wait(&ctl->q_empty[qs], qph ^ 1u, abort_flag);
           if (q_ok) {
             t = t_mine < total_tiles ? t_mine : -1;
-            ctl->q_tile[qs] = t;
-            ptx::st_shared_cluster_u32(&ctl->q_tile[qs], 1, (uint32_t)t);
+            e = t >= 0 ? upper_bound_expert(tab.prefix, num_experts, t) : 0;
+            ctl->q_item[qs] = make_int2(t, e);
             ptx::mbar_arrive(&ctl->q_full[qs]);
-            ptx::mbar_arrive_cluster(&ctl->q_full[qs], 1);
+            ptx::send_u64_to_cluster_cta(&ctl->q_item[qs], &ctl->q_full[qs], 1, (uint32_t)t, (uint32_t)e);
             // the following index is requested now; its round trip to L2 hides behind this item's loads
             if (t >= 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : t_mine + num_pairs;
           }
         }
         q_ok = __shfl_sync(0xffffffffu, (int)q_ok, 0) != 0;
         t = __shfl_sync(0xffffffffu, t, 0);
+        e = __shfl_sync(0xffffffffu, e, 0);
       } else {
         q_ok = __all_sync(0xffffffffu, ptx::mbar_wait_cluster(&ctl->q_full[qs], qph, abort_flag));
         if (q_ok) {
-          t = ctl->q_tile[qs];
+          t = ctl->q_item[qs].x;
+          e = ctl->q_item[qs].y;
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_cluster(&ctl->q_empty[qs], 0);
         }
@@ -279,29 +312,29 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         break;
       }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
+      const TileInfo ti = decode_tile(t, e, tab, n, n_pairs);
       const int half0 = ti.n0 >> 1, half1 = ti.n1 >> 1;     // token rows of each sub-tile held by each CTA
       const int xi0 = box_index(half0), xi1 = box_index(half1);
       const uint32_t tx = 2u * (W_BYTES + box_rows_of(xi0) * TILE_K + (ti.n1 ? box_rows_of(xi1) * TILE_K : 0u) +
-                                SFW_BYTES + (uint32_t)ti.n_atoms * 512u);
+                                SFW_BYTES + SFX_BYTES);
       int nt = ti.np * 2 + (int)rank;
       const int w_row = ti.e * n + nt * TILE_N;             // may run past the expert when n/128 is odd: not stored
       if (nt >= n_tiles) nt = n_tiles - 1;                  // keep the scale-atom load inside the buffer
       const int sfw_atom = ti.e * sfw_atoms_per_expert + nt * kt_count;
-      const int bs_off = blockscale_offsets[ti.e];          // a multiple of 128 (checked by the scan)
-      const int sfx_atom = ((bs_off >> 7) + ti.atom0) * kt_count;
-      // this lane's load: 0 weights, 1 tokens of sub-tile 0, 2 tokens of sub-tile 1, 3 weight scales,
-      // 4..6 token scale atoms
-      const bool active = lane == 0 || lane == 1 || (lane == 2 && ti.n1 > 0) || lane == 3 ||
-                          (lane >= 4 && lane < 4 + ti.n_atoms);
+      const int bs_off = tab.scale0(ti.e);                  // a multiple of 128 (checked by the scan)
+      const int sfx_atom_row = (bs_off >> 7) + ti.atom0;
+      // this lane's load: 0 weights, 1 tokens of sub-tile 0, 2 tokens of sub-tile 1, 3 weight scales, 4 the three
+      // token scale atoms of the item (one load: the lanes of a warp issue their loads one after the other, ~75
+      // cycles each, and the producer's issue time per K step is part of every stage's turnaround)
+      const bool active = lane == 0 || lane == 1 || (lane == 2 && ti.n1 > 0) || lane == 3 || lane == 4;
       const CUtensorMap* my_map = lane == 0 ? &maps.w : lane == 1 ? &maps.x[xi0] : lane == 2 ? &maps.x[xi1]
                                   : lane == 3 ? &maps.sfw : &maps.sfx;
       const uint32_t my_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)W_BYTES : lane == 2 ? (uint32_t)(W_BYTES + X_BYTES)
                               : lane == 3 ? (uint32_t)(W_BYTES + 2 * X_BYTES)
-                                          : (uint32_t)(W_BYTES + 2 * X_BYTES + SFW_BYTES + (lane - 4) * 512);
+                                          : (uint32_t)(W_BYTES + 2 * X_BYTES + SFW_BYTES);
       const int my_c1 = lane == 0 ? w_row : lane == 1 ? ti.row0 + (int)rank * half0
                         : lane == 2 ? ti.row0 + SUB_TILE + (int)rank * half1
-                        : lane == 3 ? sfw_atom : sfx_atom + (lane - 4) * kt_count;
+                        : lane == 3 ? sfw_atom : sfx_atom_row;
       const uint64_t my_hint = lane < 3 ? ptx::kL2EvictLast : ptx::kL2EvictNormal;
       bool ok = true;
       for (int kt = 0; kt < kt_count; ++kt) {
@@ -311,8 +344,9 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         if (rank == 0 && lane == 0) ptx::mbar_arrive_expect_tx(&ctl->full[s], tx);
         __syncwarp();
         if (active)
-          ptx::tma_load_2d_pair_hint(stage + my_off, my_map, &ctl->full[s], lane < 3 ? kt * TILE_K : 0,
-                                     lane < 3 ? my_c1 : my_c1 + kt, my_hint);
+          ptx::tma_load_2d_pair_hint(stage + my_off, my_map, &ctl->full[s],
+                                     lane < 3 ? kt * TILE_K : lane == 3 ? 0 : kt * 128,
+                                     lane == 3 ? my_c1 + kt : my_c1, my_hint);
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
       if (!ok) {
@@ -338,11 +372,12 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
           atomicOr(&g_status, ERR_MMA);
           break;
         }
-        const int t = ctl->q_tile[qs];
+        const int t = ctl->q_item[qs].x;
+        const int e = ctl->q_item[qs].y;
         ptx::mbar_arrive(&ctl->q_empty[qs]);
         if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
+        const TileInfo ti = decode_tile(t, e, tab, n, n_pairs);
         const uint32_t n_mma = sub == 0 ? ti.n0 : ti.n1;
         const uint32_t d_acc = tmem_base + sub * ACC_COLS;
         for (int kt = 0; ok && kt < kt_count; ++kt) {
@@ -389,11 +424,12 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
           atomicOr(&g_status, ERR_SCALE_COPY);
           break;
         }
-        const int t = ctl->q_tile[qs];
+        const int t = ctl->q_item[qs].x;
+        const int e = ctl->q_item[qs].y;
         ptx::mbar_arrive(&ctl->q_empty[qs]);
         if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
+        const TileInfo ti = decode_tile(t, e, tab, n, n_pairs);
         for (int kt = 0; kt < kt_count; ++kt) {
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
@@ -413,13 +449,27 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (both CTAs), both accumulators at
-    // the same time: warps 2..9 drain accumulator 0, warps 10..17 accumulator 1; the two warps of a lane quadrant take alternate
-    // 32-column chunks
+    // ------------------------------------------------------------------ epilogue (both CTAs), 16 warps: four per
+    // TMEM lane quadrant share the twelve 32-column chunks of an item's two accumulators, three each (two of one
+    // accumulator and one of the other).  A warp reads its chunks of accumulator 0 into registers (converted), hands
+    // accumulator 0 back, does the same for accumulator 1, and stores afterwards: both accumulators of an item
+    // complete together, the MMA lanes get them back after ~two TMEM reads each instead of after the stores (which
+    // take several thousand cycles per item), and the next item's MMAs run during the stores.
+    //   slot 0: accumulator 0, columns 32 idx          slot 1: idx < 2 ? accumulator 0, columns 32 idx + 128
+    //   slot 2: idx < 2 ? accumulator 1, columns 32 (idx + 2)              : accumulator 1, columns 32 (idx - 2)
+    //                   : accumulator 1, columns 32 (idx - 2) + 128
     const int q = warp & 3;
-    const int sub = (warp - 2) >> 3;
-    const int half = ((warp - 2) >> 2) & 1;
-    uint32_t full_ph = 0, qph = 0;
+    const int idx = (warp - 2) >> 2;      // 0..3 within the lane quadrant
+    const bool low = idx < 2;
+    const int col0 = idx * 32;
+    const int col1 = low ? idx * 32 + 128 : (idx - 2) * 32;
+    const int col2 = low ? (idx + 2) * 32 : (idx - 2) * 32 + 128;
+    OutT* stage_warp = reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * (EPI_BYTES_PER_WARP / 2);
+    // HOLD = false (chosen by the host for one or two K steps per item): each chunk is stored right after it is read.
+    // Such a call is bound by the output stores themselves (n x k is small against the m x n output) and holding only
+    // adds concurrent load traffic to them (measured at k = 256: 1.03 ms held, 0.71 ms not).
+    uint32_t full_ph = 0, qph = 0;        // both accumulators' barriers advance once per item that uses them
+    uint32_t full1_ph = 0;
     int qs = 0;
     while (true) {
       const bool have = rank == 0 ? ptx::mbar_wait(&ctl->q_full[qs], qph, abort_flag)
@@ -431,18 +481,38 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
         }
         break;
       }
-      const int t = ctl->q_tile[qs];
+      const int t = ctl->q_item[qs].x;
+      const int e = ctl->q_item[qs].y;
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive_cluster(&ctl->q_empty[qs], 0);   // leader's barrier
       if (++qs == QUEUE_DEPTH) { qs = 0; qph ^= 1u; }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, n, n_pairs);
-      if (sub == 1 && ti.n1 == 0) continue;               // an item of <= 192 rows does not use accumulator 1
+      const TileInfo ti = decode_tile(t, e, tab, n, n_pairs);
       const int nt = ti.np * 2 + (int)rank;
       const bool store = nt < n_tiles;
-      const int n_mma = sub == 0 ? ti.n0 : ti.n1;
-      const int valid = sub == 0 ? ti.v0 : ti.v1;
-      const bool got = ptx::mbar_wait(&ctl->tmem_full[sub], full_ph, abort_flag);
+      const bool store_now = !HOLD && store;
+      const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+      uint32_t held0[16], held1[16], held2[16];
+      // which of this warp's chunks exist in this item (warp-uniform)
+      const bool has0 = col0 < ti.n0;
+      const bool has1 = low ? col1 < ti.n0 : col1 < ti.n1;
+      const bool has2 = col2 < ti.n1;
+      // token row (within the item) of each slot's first column
+      const int tok0 = col0;
+      const int tok1 = low ? col1 : SUB_TILE + col1;
+      const int tok2 = SUB_TILE + col2;
+      const int col_off = nt * TILE_N + q * 32;
+      auto store_slot = [&](const uint32_t (&held)[16], int tok) {
+        if (scatter.meta == nullptr) {
+          uint16_t* out = reinterpret_cast<uint16_t*>(d + (int64_t)(ti.row0 + tok) * n + col_off);
+          store_held_chunk_dense(held, out, n, ti.valid - tok, lane);
+        } else {
+          // lane l fetches the destination of token l of the chunk
+          OutT* dest = scatter_row_ptr<OutT>(scatter, ti.row0 + tok + lane, tok + lane < ti.valid, n, col_off, &g_status);
+          store_held_chunk_scatter<OutT>(held, stage_warp, dest, lane);
+        }
+      };
+      bool got = ptx::mbar_wait(&ctl->tmem_full[0], full_ph, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) {
           *abort_flag = 1;
@@ -452,16 +522,45 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
       }
       full_ph ^= 1u;
       ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + sub * ACC_COLS + ((uint32_t)(q * 32) << 16);
-      OutT* dst = d + (int64_t)(ti.row0 + sub * SUB_TILE) * n + (nt * TILE_N + q * 32);
-      drain_accumulator_shared<OutT, EPI_TOK>(
-          taddr, n_mma, valid, reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * (EPI_TOK * 32), dst, n, store, lane,
-          [&] {
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[sub], 0);   // leader's barrier
-          },
-          scatter, ti.row0 + sub * SUB_TILE, nt * TILE_N + q * 32, &g_status, half * 32, 64);
+      if (has0) {
+        read_held_chunk<OutT>(lane_base + col0, held0);
+        if (store_now) store_slot(held0, tok0);
+      }
+      if (low && has1) {
+        read_held_chunk<OutT>(lane_base + col1, held1);
+        if (store_now) store_slot(held1, tok1);
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[0], 0);     // leader's barrier
+      if (ti.n1 > 0) {                                      // an item of <= 192 rows does not use accumulator 1
+        got = ptx::mbar_wait(&ctl->tmem_full[1], full1_ph, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) {
+            *abort_flag = 1;
+            atomicOr(&g_status, ERR_EPILOGUE);
+          }
+          break;
+        }
+        full1_ph ^= 1u;
+        ptx::tc_fence_after_sync();
+        if (!low && has1) {
+          read_held_chunk<OutT>(lane_base + ACC_COLS + col1, held1);
+          if (store_now) store_slot(held1, tok1);
+        }
+        if (has2) {
+          read_held_chunk<OutT>(lane_base + ACC_COLS + col2, held2);
+          if (store_now) store_slot(held2, tok2);
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(&ctl->tmem_empty[1], 0);
+      }
+      if (HOLD && store) {
+        if (has0) store_slot(held0, tok0);
+        if (has1) store_slot(held1, tok1);
+        if (has2) store_slot(held2, tok2);
+      }
     }
   }
 
@@ -475,9 +574,9 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
 }
 
-template <typename OutT>
-int launch(const mm::CallArgs& c, int min_rows, int cluster_cap, bool first_of_call, bool last_of_call,
-           uint32_t* earlier_ctas) {
+template <typename OutT, bool HOLD>
+int launch_as(const mm::CallArgs& c, int min_rows, int cluster_cap, bool first_of_call, bool last_of_call,
+              uint32_t* earlier_ctas) {
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
@@ -493,12 +592,12 @@ int launch(const mm::CallArgs& c, int min_rows, int cluster_cap, bool first_of_c
   }
   rc = make_tensormap_records512(&maps.sfw, c.sfb, (uint64_t)c.num_experts * (c.n / TILE_N) * kt_count);
   if (rc != ES_B200_OK) return rc;
-  // whole 128-row atoms only; loads past the end read as zero (a map needs at least one record)
-  const uint64_t sfx_records = (uint64_t)(c.sfa_rows / 128) * kt_count;
-  rc = make_tensormap_records512(&maps.sfx, c.sfa, sfx_records ? sfx_records : 1);
+  // whole 128-row atoms only; loads past the end read as zero (a map needs at least one row)
+  const uint64_t sfx_rows = (uint64_t)(c.sfa_rows / 128);
+  rc = make_tensormap_record_columns(&maps.sfx, c.sfa, sfx_rows ? sfx_rows : 1, (uint64_t)kt_count, 3);
   if (rc != ES_B200_OK) return rc;
 
-  auto kernel = mxfp8_grouped_mm_pair_kernel<OutT>;
+  auto kernel = mxfp8_grouped_mm_pair_kernel<OutT, HOLD>;
   static bool configured[64] = {false};
   int dev = 0;
   ES_CUDA_TRY(cudaGetDevice(&dev));
@@ -541,6 +640,14 @@ int launch(const mm::CallArgs& c, int min_rows, int cluster_cap, bool first_of_c
                                  *earlier_ctas));
   *earlier_ctas += 2u * (uint32_t)clusters;
   return ES_B200_OK;
+}
+
+// items of one or two K steps store each chunk as soon as it is read (see the epilogue)
+template <typename OutT>
+int launch(const mm::CallArgs& c, int min_rows, int cluster_cap, bool first_of_call, bool last_of_call,
+           uint32_t* earlier_ctas) {
+  return c.k / TILE_K > 2 ? launch_as<OutT, true>(c, min_rows, cluster_cap, first_of_call, last_of_call, earlier_ctas)
+                          : launch_as<OutT, false>(c, min_rows, cluster_cap, first_of_call, last_of_call, earlier_ctas);
 }
 
 int launch_bf16(const mm::CallArgs& c, int min_rows, int max_clusters, bool first_of_call, bool last_of_call,

@@ -32,7 +32,7 @@ inline int get_encode_fn(EncodeTiledFn* out) {
 struct MapCacheEntry {
   const void* base;
   uint64_t rows, row_bytes;
-  uint32_t box_rows, kind;      // kind 0: byte matrix with 128-byte swizzle, 1: 512-byte records
+  uint32_t box_rows, kind;      // kind 0: byte matrix with 128-byte swizzle, 1: 512-byte records, 2: columns of such records
   bool valid;
   CUtensorMap map;
 };
@@ -95,6 +95,32 @@ inline int make_tensormap_records512(CUtensorMap* map, const void* base, uint64_
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(ES_B200_ERR_CUDA, "cuTensorMapEncodeTiled (records) failed with CUresult %d", (int)r);
   *slot = MapCacheEntry{base, count, 512, 1, 1, true, *map};
+  return ES_B200_OK;
+}
+
+// The same records viewed as [rows, per_row x 128] uint32 — record (r, j) at index r * per_row + j — with a box of one
+// record in j and `box_rows` rows: ONE load fetches the records (r .. r + box_rows - 1, j), 512 bytes each,
+// contiguous in shared memory (rows past the end read as zero).
+inline int make_tensormap_record_columns(CUtensorMap* map, const void* base, uint64_t rows, uint64_t per_row,
+                                         uint32_t box_rows) {
+  MapCacheEntry* slot = map_cache_slot(base, rows, 512 * per_row, box_rows, 2);
+  if (map_cache_hit(slot, base, rows, 512 * per_row, box_rows, 2)) {
+    *map = slot->map;
+    return ES_B200_OK;
+  }
+  EncodeTiledFn fn;
+  int rc = get_encode_fn(&fn);
+  if (rc != ES_B200_OK) return rc;
+  cuuint64_t dims[2] = {128 * per_row, rows};
+  cuuint64_t strides[1] = {512 * per_row};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(ES_B200_ERR_CUDA, "cuTensorMapEncodeTiled (record columns) failed with CUresult %d", (int)r);
+  *slot = MapCacheEntry{base, rows, 512 * per_row, box_rows, 2, true, *map};
   return ES_B200_OK;
 }
 
