@@ -193,4 +193,50 @@ __device__ __forceinline__ int upper_bound_expert(const int* prefix, int n, int 
   return lo;
 }
 
+// ---- device: per-expert facts in shared memory ------------------------------------------------
+// Every role of a grouped GEMM kernel needs the expert's row count, first row and first scale row for every work
+// item.  Read from global memory that is a chain of dependent L2 round trips per item (~2000 cycles behind the binary
+// search over the item prefix), which an MMA-issuing lane cannot hide when an item has only a few K steps.  The
+// kernels therefore copy them once per CTA into the tail of the array that holds the item prefix: `table` has
+// ES_B200_MAX_EXPERTS + 1 ints, the prefix takes n + 1 of them, the copies of as many experts as fit follow (all of
+// them when n <= 256 with three tables); experts beyond that are read from global memory as before.
+struct ExpertTable {
+  const int* prefix;
+  const int* rows;              // shared-memory copies for experts below `cached`
+  const int* first_row;
+  const int* scale_row0;
+  int cached;
+  const int* problem_sizes;     // global memory
+  const int* expert_offsets;
+  const int* blockscale_offsets;   // may be null (no third table)
+  __device__ __forceinline__ int m(int e) const { return e < cached ? rows[e] : problem_sizes[e * 3]; }
+  __device__ __forceinline__ int row0(int e) const { return e < cached ? first_row[e] : expert_offsets[e]; }
+  __device__ __forceinline__ int scale0(int e) const { return e < cached ? scale_row0[e] : blockscale_offsets[e]; }
+};
+// Called by all threads after block_exclusive_scan has written table[0..n]; the caller synchronises the block before
+// the table is read.
+__device__ __forceinline__ ExpertTable fill_expert_table(int* table, int n, const int* problem_sizes,
+                                                         const int* expert_offsets, const int* blockscale_offsets) {
+  ExpertTable tab;
+  const int tables = blockscale_offsets ? 3 : 2;
+  const int room = (ES_B200_MAX_EXPERTS + 1 - (n + 1)) / tables;
+  tab.cached = n < room ? n : room;
+  int* rows = table + n + 1;
+  int* first_row = rows + tab.cached;
+  int* scale_row0 = first_row + tab.cached;
+  for (int e = threadIdx.x; e < tab.cached; e += blockDim.x) {
+    rows[e] = problem_sizes[e * 3];
+    first_row[e] = expert_offsets[e];
+    if (blockscale_offsets) scale_row0[e] = blockscale_offsets[e];
+  }
+  tab.prefix = table;
+  tab.rows = rows;
+  tab.first_row = first_row;
+  tab.scale_row0 = scale_row0;
+  tab.problem_sizes = problem_sizes;
+  tab.expert_offsets = expert_offsets;
+  tab.blockscale_offsets = blockscale_offsets;
+  return tab;
+}
+
 }  // namespace es_b200

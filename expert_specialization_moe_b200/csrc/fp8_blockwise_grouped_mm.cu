@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include "common.cuh"
 #include "epilogue.cuh"
 #include "sm100_ptx.cuh"
@@ -58,7 +59,7 @@ struct SharedCtl {
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
-  int tile_prefix[ES_B200_MAX_EXPERTS + 1];
+  int tile_prefix[ES_B200_MAX_EXPERTS + 1];   // item prefix [0, E], then the per-expert tables (fill_expert_table)
 };
 
 template <int TOK_TILE_, int STAGES_, int NCH_, int LOADERS_, int GROUPS_>
@@ -99,22 +100,41 @@ struct TileInfo {
   int e, tt, nt, valid, n_mma, row0;
 };
 
+// A work item is `group` consecutive weight tiles of one (expert, token tile); a CTA takes the items blockIdx.x,
+// blockIdx.x + gridDim.x, ... and every role walks their tiles in the same order.  The item is decoded once (binary
+// search over the item prefix, a division) and the tiles inside it only advance `nt`: with two K blocks per tile
+// (k = 256) every role spent more time per tile finding out what the tile was than working on it (measured: the
+// producer lane and both MMA lanes ~2200 cycles per tile, almost none of it waiting).
 template <int TOK_TILE>
-__device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
-                                                const int* expert_offsets) {
+struct TileWalk {
   TileInfo ti;
-  ti.e = upper_bound_expert(prefix, num_experts, t);
-  const int i = t - prefix[ti.e];
-  const int m = problem_sizes[ti.e * 3];
-  const int token_tiles = (m + TOK_TILE - 1) / TOK_TILE;
-  ti.nt = i / token_tiles;
-  ti.tt = i - ti.nt * token_tiles;
-  const int rem = m - ti.tt * TOK_TILE;
-  ti.valid = rem < TOK_TILE ? rem : TOK_TILE;
-  ti.n_mma = (ti.valid + 15) & ~15;
-  ti.row0 = expert_offsets[ti.e] + ti.tt * TOK_TILE;
-  return ti;
-}
+  int item, left;
+  __device__ __forceinline__ TileWalk() : item((int)blockIdx.x - (int)gridDim.x), left(0) {}
+  // advances to this CTA's next tile; false when there is none
+  __device__ __forceinline__ bool next(const ExpertTable& tab, int num_experts, int total_items, int n_tiles, int group) {
+    if (left > 0) {
+      --left;
+      ++ti.nt;
+      return true;
+    }
+    item += (int)gridDim.x;
+    if (item >= total_items) return false;
+    ti.e = upper_bound_expert(tab.prefix, num_experts, item);
+    const int i = item - tab.prefix[ti.e];
+    const int m = tab.m(ti.e);
+    const int token_tiles = (m + TOK_TILE - 1) / TOK_TILE;
+    const int ng = i / token_tiles;
+    ti.tt = i - ng * token_tiles;
+    ti.nt = ng * group;
+    const int rem = m - ti.tt * TOK_TILE;
+    ti.valid = rem < TOK_TILE ? rem : TOK_TILE;
+    ti.n_mma = (ti.valid + 15) & ~15;
+    ti.row0 = tab.row0(ti.e) + ti.tt * TOK_TILE;
+    const int rest = n_tiles - ti.nt;
+    left = (rest < group ? rest : group) - 1;
+    return true;
+  }
+};
 
 template <typename OutT, class S>
 __global__ void __launch_bounds__(S::THREADS, 1)
@@ -123,7 +143,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
                                 const __grid_constant__ CUtensorMap map_x128, const float* __restrict__ scales_a,
                                 const float* __restrict__ scales_b, OutT* __restrict__ d,
                                 const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                                int num_experts, int n, int k, int min_rows, int max_rows, int wait_at_start) {
+                                int num_experts, int n, int k, int min_rows, int max_rows, int wait_at_start, int group) {
   constexpr int TOK = S::TOK_TILE;
   constexpr int STAGES = S::STAGES;
   constexpr int NCH = S::NCH;
@@ -169,15 +189,25 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
   const int n_tiles = n / TILE_N;
   block_exclusive_scan(num_experts, ctl->tile_prefix, ctl->warp_sums, [&](int e) {
     const int m = problem_sizes[e * 3];
-    return (m > 0 && m >= min_rows && m <= max_rows) ? ((m + TOK - 1) / TOK) * n_tiles : 0;
+    return (m > 0 && m >= min_rows && m <= max_rows) ? ((m + TOK - 1) / TOK) * ((n_tiles + group - 1) / group) : 0;
   });
+  // a launch without work (the host only knows an upper bound of the rows per expert) ends here
+  if (ctl->tile_prefix[num_experts] == 0) {
+    pdl_launch_dependents();
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) ptx::tmem_dealloc(ctl->tmem_base, S::TMEM_COLS);
+    if (!wait_at_start) pdl_wait_prior_grid();
+    return;
+  }
+  const ExpertTable tab = fill_expert_table(ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, nullptr);
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
   pdl_launch_dependents();
 
   const uint32_t tmem_base = ctl->tmem_base;
-  const int total_tiles = ctl->tile_prefix[num_experts];
+  const int total_items = ctl->tile_prefix[num_experts];
   volatile int* abort_flag = &ctl->abort_flag;
 
   if (warp == 0) {
@@ -186,8 +216,9 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      TileWalk<TOK> walk;
+      while (ok && walk.next(tab, num_experts, total_items, n_tiles, group)) {
+        const TileInfo& ti = walk.ti;
         const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_x128;
         const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : 128u;
         const uint32_t tx = W_BYTES + box_rows * TILE_K;
@@ -214,8 +245,9 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
       const int mine = warp - 1;
       int g = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      TileWalk<TOK> walk;
+      while (ok && walk.next(tab, num_experts, total_items, n_tiles, group)) {
+        const TileInfo& ti = walk.ti;
         const uint32_t idesc = ptx::make_idesc_f8(TILE_N, ti.n_mma);
         for (int kt = 0; kt < kt_count; ++kt, ++g) {
           if ((g & 1) != mine) continue;
@@ -249,11 +281,12 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
     const int mine = warp - 3;
     int c = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+    TileWalk<TOK> walk;
+    while (ok && walk.next(tab, num_experts, total_items, n_tiles, group)) {
       const int chunks_in_tile = (kt_count + CH_KT - 1) / CH_KT;
       // this warp's chunks of the tile: c, c+1, .. with (c & 1) == mine
-      if (chunks_in_tile == 1 && (c & LMASK) != mine) { ++c; continue; }   // common for small K: skip the decode too
-      const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      if (chunks_in_tile == 1 && (c & LMASK) != mine) { ++c; continue; }   // common for small K
+      const TileInfo& ti = walk.ti;
       const float* sb_row = scales_b + ((int64_t)ti.e * n_tiles + ti.nt) * kt_count;
       for (int kt0 = 0; kt0 < kt_count; kt0 += CH_KT, ++c) {
         if ((c & LMASK) != mine) continue;
@@ -300,7 +333,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
     // are strictly serial (turn barriers): a group that waited on part_full / chunk_full for a tile further ahead
     // would be more than one phase ahead of those barriers, and a parity wait cannot tell phases n and n+2 apart.
     const int q = warp & 3;                           // TMEM lane quadrant of this warp
-    const int group = (warp - S::FIRST_EPI_WARP) / S::GROUP_WARPS;
+    const int egroup = (warp - S::FIRST_EPI_WARP) / S::GROUP_WARPS;
     const int col0 = (((warp - S::FIRST_EPI_WARP) % S::GROUP_WARPS) >> 2) * 32;   // this warp's 32 token columns
     OutT* stage_warp = reinterpret_cast<OutT*>(epi_stage) + (warp - S::FIRST_EPI_WARP) * (EPI_TOK * 32);
     const int part = lane & 3;
@@ -309,20 +342,22 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
     bool alive = true;
     uint32_t turn_ph = 0;
     int tile_index = 0;
-    for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x, ++tile_index) {
-      if ((tile_index & (S::GROUPS - 1)) != group) {   // the other group's tile
+    TileWalk<TOK> walk;
+    while (alive && walk.next(tab, num_experts, total_items, n_tiles, group)) {
+      const int my_index = tile_index++;
+      if ((my_index & (S::GROUPS - 1)) != egroup) {   // the other group's tile
         g += kt_count;
         c += (kt_count + CH_KT - 1) / CH_KT;
         continue;
       }
-      const TileInfo ti = decode_tile<TOK>(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const TileInfo& ti = walk.ti;
       const bool has_cols = col0 < ti.n_mma;          // warp-uniform: a set past the tile's tokens only keeps the
                                                       // barriers moving
       float acc[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-      if (S::GROUPS == 2 && tile_index > 0) {          // the other group has left the K loop of the previous tile
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctl->turn[group], turn_ph, abort_flag))) {
+      if (S::GROUPS == 2 && my_index > 0) {            // the other group has left the K loop of the previous tile
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&ctl->turn[egroup], turn_ph, abort_flag))) {
           if (lane == 0) {
             *abort_flag = 1;
             atomicOr(&g_status, ERR_EPILOGUE);
@@ -376,7 +411,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
       if (!alive) break;
       if (S::GROUPS == 2) {
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&ctl->turn[group ^ 1]);
+        if (lane == 0) ptx::mbar_arrive(&ctl->turn[egroup ^ 1]);
       }
       // output: this warp's 32 tokens x 32 n, 16 tokens at a time through its 1 KB tile, 128-bit stores (4 lanes per
       // 64-byte row piece)
@@ -433,8 +468,14 @@ int launch(const void* a, const void* b, const float* sa, const float* sb, void*
     ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES));
     configured[dev & 63] = true;
   }
-  const int64_t max_tiles = ((num_rows + S::TOK_TILE - 1) / S::TOK_TILE + num_experts) * (int64_t)(n / TILE_N);
-  const int grid = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
+  // weight tiles per work item: the per-item work of every role (decode) is spread over ~8 K blocks
+  const int kt_count = k / TILE_K;
+  static const int group_blocks = getenv("ES_DBG_GROUP_BLOCKS") ? atoi(getenv("ES_DBG_GROUP_BLOCKS")) : 8;   // DEBUG
+  int group = (group_blocks + kt_count - 1) / kt_count;
+  if (group < 1) group = 1;
+  const int64_t max_items = ((num_rows + S::TOK_TILE - 1) / S::TOK_TILE + num_experts) *
+                            (int64_t)((n / TILE_N + group - 1) / group);
+  const int grid = (int)(max_items < info.sm_count ? max_items : info.sm_count);
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -448,7 +489,7 @@ int launch(const void* a, const void* b, const float* sa, const float* sb, void*
   cfg.numAttrs = 1;
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sa, sb,
                                  static_cast<OutT*>(d), ps, eo, num_experts, n, k, min_rows, max_rows,
-                                 first_of_call ? 1 : 0));
+                                 first_of_call ? 1 : 0, group));
   return ES_B200_OK;
 }
 

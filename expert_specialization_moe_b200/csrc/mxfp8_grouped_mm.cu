@@ -77,9 +77,9 @@ struct Shape {
   static constexpr int TOK_TILE = TOK_TILE_;     // token rows per tile (tcgen05.mma N, runtime multiple of 16)
   static constexpr int STAGES = STAGES_;
   static constexpr int LANES = LANES_;
-  // odd ring slots by cp.async: pays where the slot is mostly weights (measured per SM on 64 CTAs: 66 vs 49 GB/s for
-  // the 32-token shape); with a 14 KB token tile per slot the 128 loader threads copy as many token bytes (L2 hits)
-  // as weight bytes and the shape is slower with it (48 vs 52 GB/s)
+  // odd ring slots by cp.async (second load path).  Alone on the GPU the 112-token shape is slower with it (its 128
+  // loader threads copy as many token bytes, L2 hits, as weight bytes: 48 vs 52 GB/s per SM) but inside a call, next to
+  // the other kernels, the call is faster with it (reference-distribution workload at 32 experts: 0.1938 vs 0.1967 ms)
   static constexpr bool SECOND_LOAD_PATH = SECOND_LOAD_PATH_;
   static constexpr int X_BYTES = TOK_TILE * TILE_K;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // W | X | weight scales | token scales
@@ -90,7 +90,7 @@ struct Shape {
   static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 };
 using ShapeTiny = Shape<32, 10, 4, true>;   // 21 KB slots; TMEM: 2 x 4 x 32 accumulator columns + 80 scale columns
-using ShapeMid = Shape<112, 6, 2, false>;   // 31 KB slots; TMEM: 2 x 2 x 112 accumulator columns + 48 scale columns
+using ShapeMid = Shape<112, 6, 2, true>;    // 31 KB slots; TMEM: 2 x 2 x 112 accumulator columns + 48 scale columns
 
 constexpr uint32_t ERR_PRODUCER = 1u, ERR_MMA = 2u, ERR_EPILOGUE = 4u, ERR_SCALE_COPY = 8u, ERR_LOADER = 0x400u;
 constexpr int QUEUE_DEPTH = 4;          // tile indices in flight between the producer lane and the other roles
@@ -107,7 +107,7 @@ struct SharedCtl {
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
-  int tile_prefix[ES_B200_MAX_EXPERTS + 1];
+  int tile_prefix[ES_B200_MAX_EXPERTS + 1];   // item prefix [0, E], then the per-expert tables (fill_expert_table)
 };
 
 template <class S>
@@ -125,14 +125,13 @@ struct TileInfo {
 };
 
 // tile t of this launch -> (expert, weight tile); one token tile per expert
-__device__ __forceinline__ TileInfo decode_tile(int t, const int* prefix, int num_experts, const int* problem_sizes,
-                                                const int* expert_offsets) {
+__device__ __forceinline__ TileInfo decode_tile(int t, const ExpertTable& tab, int num_experts) {
   TileInfo ti;
-  ti.e = upper_bound_expert(prefix, num_experts, t);
-  ti.nt = t - prefix[ti.e];
-  ti.valid = problem_sizes[ti.e * 3];
+  ti.e = upper_bound_expert(tab.prefix, num_experts, t);
+  ti.nt = t - tab.prefix[ti.e];
+  ti.valid = tab.m(ti.e);
   ti.n_mma = (ti.valid + 15) & ~15;
-  ti.row0 = expert_offsets[ti.e];
+  ti.row0 = tab.row0(ti.e);
   return ti;
 }
 
@@ -226,6 +225,18 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     }
     return n_tiles;
   });
+  // A launch without work (the host only knows an upper bound of the rows per expert) ends here: the kernels of a call
+  // run one after the other on every SM, and an empty one that ran its roles through the empty queue cost ~5 us of
+  // every call (an empty four-kernel call: 22 us on the GPU, 14 us with this exit).
+  if (ctl->tile_prefix[num_experts] == 0) {
+    pdl_launch_dependents();
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) ptx::tmem_dealloc(ctl->tmem_base, TMEM_COLS);
+    end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
+    return;
+  }
+  const ExpertTable tab = fill_expert_table(ctl->tile_prefix, num_experts, problem_sizes, expert_offsets, blockscale_offsets);
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
@@ -269,14 +280,14 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         break;
       }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const TileInfo ti = decode_tile(t, tab, num_experts);
       const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_xt;
       const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : (uint32_t)TOK_TILE;
       const uint32_t tx = W_BYTES + box_rows * TILE_K + 2 * SF_BYTES;
       // this lane's load: 0 weight tile (streamed once: evict first), 1 token tile (re-read by every weight tile of
       // the expert: evict last), 2 weight scale atom, 3 token scale atom (512-byte records, index = atom number)
       const int sfw_atom = (ti.e * n_tiles + ti.nt) * kt_count;
-      const int sfx_atom = (blockscale_offsets[ti.e] >> 7) * kt_count;
+      const int sfx_atom = (tab.scale0(ti.e) >> 7) * kt_count;
       const CUtensorMap* my_map = lane == 0 ? &map_w : lane == 1 ? xm : lane == 2 ? &map_sfw : &map_sfx;
       const uint32_t my_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)W_BYTES
                               : lane == 2 ? (uint32_t)(W_BYTES + X_BYTES) : (uint32_t)(W_BYTES + X_BYTES + SF_BYTES);
@@ -318,7 +329,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         int t;
         if (!q.next<false>(ctl, abort_flag, lane, &t)) { ok = false; break; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile(t, tab, num_experts);
         if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * S::ACC_COLS + mma_lane * TOK_TILE;
@@ -399,11 +410,11 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         int t;
         if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+        const TileInfo ti = decode_tile(t, tab, num_experts);
         const uint8_t* w_src = w_codes + ((int64_t)ti.e * n + ti.nt * TILE_N + r0) * k + c16 * 16;
         const uint8_t* x_src = a_codes + ((int64_t)ti.row0 + r0) * k + c16 * 16;
         const int64_t sfw_off = ((int64_t)(ti.e * n_tiles + ti.nt) * kt_count) * SF_BYTES;
-        const int64_t sfx_off = ((int64_t)(blockscale_offsets[ti.e] >> 7) * kt_count) * SF_BYTES;
+        const int64_t sfx_off = ((int64_t)(tab.scale0(ti.e) >> 7) * kt_count) * SF_BYTES;
         // the two scale atoms are 64 pieces: threads 0..31 the weight atom, 32..63 the token atom (zeros past the buffer)
         const uint8_t* sf_src = lt < 32 ? sf_weights + sfw_off + lt * 16 : sf_tokens + sfx_off + (lt - 32) * 16;
         const bool sf_in_range = lt < 32 || sfx_off + (int64_t)kt_count * SF_BYTES <= sf_token_bytes;
@@ -450,7 +461,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       int t;
       if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, ctl->tile_prefix, num_experts, problem_sizes, expert_offsets);
+      const TileInfo ti = decode_tile(t, tab, num_experts);
       const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       ptx::tc_fence_after_sync();

@@ -90,26 +90,8 @@ struct SharedCtl {
   uint32_t tmem_base;
   int abort_flag;
   int warp_sums[32];
-  // [0, E]: exclusive prefix of the experts' item counts; behind it, as far as the array reaches (all experts when
-  // E <= 256), three tables of the first `cached` experts: token rows, first row, first scale row
+  // [0, E]: exclusive prefix of the experts' item counts; behind it the per-expert tables (fill_expert_table)
   int table[ES_B200_MAX_EXPERTS + 1];
-};
-
-// Per-expert facts that every role needs for every work item.  Reading them from global memory cost each role
-// ~2000 cycles per item (dependent L2 round trips behind a binary search), which the MMA lanes cannot hide: with
-// K = 768 an item is only ~5000 cycles of tensor work.  They are copied to shared memory once per CTA.
-struct ExpertTable {
-  const int* prefix;
-  const int* rows;         // shared-memory copies for experts below `cached`
-  const int* first_row;
-  const int* scale_row0;
-  int cached;
-  const int* problem_sizes;     // global memory, for experts at or above `cached`
-  const int* expert_offsets;
-  const int* blockscale_offsets;
-  __device__ __forceinline__ int m(int e) const { return e < cached ? rows[e] : problem_sizes[e * 3]; }
-  __device__ __forceinline__ int row0(int e) const { return e < cached ? first_row[e] : expert_offsets[e]; }
-  __device__ __forceinline__ int scale0(int e) const { return e < cached ? scale_row0[e] : blockscale_offsets[e]; }
 };
 
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + EPI_WARPS * EPI_BYTES_PER_WARP + sizeof(SharedCtl);
@@ -210,10 +192,6 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
 #pragma unroll
     for (int i = 0; i < 5; ++i) ptx::prefetch_tensormap(&maps.x[i]);
   }
-  if (warp == 1) {
-    ptx::tmem_alloc_pair(&ctl->tmem_base, TMEM_COLS);
-    ptx::tmem_relinquish_pair();
-  }
   // This kernel is chained with the single-CTA kernels of the same call by programmatic dependent launch — behind
   // them, and for a large call also in front of them with a capped grid.  The first kernel of the call waits for
   // everything before it (griddepcontrol.wait) before it lets the others start, so the operands are final; the
@@ -233,26 +211,18 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
     }
     return ((m + TOK_TILE - 1) / TOK_TILE) * n_pairs;
   });
-  ExpertTable tab;
-  {
-    const int room = (ES_B200_MAX_EXPERTS + 1 - (num_experts + 1)) / 3;
-    tab.cached = num_experts < room ? num_experts : room;
-    int* rows = ctl->table + num_experts + 1;
-    int* first_row = rows + tab.cached;
-    int* scale_row0 = first_row + tab.cached;
-    for (int e = threadIdx.x; e < tab.cached; e += THREADS) {
-      rows[e] = problem_sizes[e * 3];
-      first_row[e] = expert_offsets[e];
-      scale_row0[e] = blockscale_offsets[e];
-    }
-    tab.prefix = ctl->table;
-    tab.rows = rows;
-    tab.first_row = first_row;
-    tab.scale_row0 = scale_row0;
-    tab.problem_sizes = problem_sizes;
-    tab.expert_offsets = expert_offsets;
-    tab.blockscale_offsets = blockscale_offsets;
+  // A launch without work (the host only knows an upper bound of the rows per expert) ends here, before it holds
+  // TMEM or has signalled its partner CTA; both CTAs of a pair see the same total.
+  if (ctl->table[num_experts] == 0) {
+    pdl_launch_dependents();
+    end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
+    return;
   }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(&ctl->tmem_base, TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  const ExpertTable tab = fill_expert_table(ctl->table, num_experts, problem_sizes, expert_offsets, blockscale_offsets);
   // barriers, TMEM and tables of both CTAs must exist before either CTA signals the other
   ptx::tc_fence_before_sync();
   ptx::cluster_sync();
