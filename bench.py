@@ -412,9 +412,9 @@ def bench_ep_layer(args, device, rank, world, dist):
                                        else "NCCL all-to-all dispatch/combine"),
                            "experts_per_gpu": e_local},
                 "clocks": clocks, "device_status": status,
-                # ours per step: dispatch-quant-push, 2 barriers, up to 3 + 3 GEMM bucket kernels, silu-quant,
-                # combine-push, weighted sum (fused) / 2 quant kernels + GEMMs (all-to-all path)
-                "gpu_launches": args.steps * ((30 if args.workload == "qwen3_ep_pipelined" else 15) if fused else 10)}
+                # ours per step: route count + tables, dispatch-quant-push, unpack, 2 barriers, 3 + 3 GEMM launches,
+                # silu-quant, weighted sum (fused) / 2 quant kernels + GEMMs (all-to-all path)
+                "gpu_launches": args.steps * ((28 if args.workload == "qwen3_ep_pipelined" else 14) if fused else 9)}
     del shard, x
     torch.cuda.empty_cache()
     return line
@@ -930,10 +930,10 @@ def main():
     elapsed_ms, e2e_ms = float(stats[0]), float(stats[1])
     flops_total, h2d_total, d2h_total = float(sums[0]), float(sums[1]), float(sums[2])
 
-    # one call launches one kernel per row-count bucket that the host-known row count can reach: <=32 rows (always),
-    # 33..128 rows, >=129 rows (CTA pairs), plus a leading capped CTA-pair launch when the call is split
+    # one call launches the streaming kernel (both shapes in one launch), the CTA-pair kernel when the host-known row
+    # count can reach its bucket (>= 113 rows at most shapes), and a leading capped CTA-pair launch when the call is split
     rows_local = int(counts.sum())
-    launches_per_step = 1 + (rows_local > 32) + (rows_local >= 129) + (rows_local >= 2048)
+    launches_per_step = 1 + (rows_local >= 113) + (rows_local >= 2048)
     line = None
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps
@@ -950,9 +950,10 @@ def main():
             "config": config,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "peak_kind": peak_kind, "algorithmic_bytes": abytes,
-                         "kernel": ("mxfp8_grouped_mm_pair_kernel (capped) | mxfp8_grouped_mm_kernel<32x10> + <128x6> | "
-                                    "mxfp8_grouped_mm_pair_kernel: one PDL chain per call, buckets side by side"
-                                    if launches_per_step == 4 else "mxfp8_grouped_mm_kernel chain"),
+                         "kernel": ("mxfp8_grouped_mm_pair_kernel (capped) | mxfp8_grouped_mm_kernel (32- and 112-token "
+                                    "shapes in one launch) | mxfp8_grouped_mm_pair_kernel: one PDL chain per call, "
+                                    "buckets side by side"
+                                    if launches_per_step == 3 else "mxfp8_grouped_mm_kernel chain"),
                          "kernel_ms": my_ms},
             "clocks": clocks, "gpu_launches": args.steps * launches_per_step, "host_us_per_call": host_us,
         }

@@ -157,19 +157,48 @@ struct QueueReader {
   }
 };
 
+// Arguments that do not depend on the tile shape
+struct KernelArgs {
+  const uint8_t* a_codes;
+  const uint8_t* w_codes;
+  const uint8_t* sf_tokens;
+  const uint8_t* sf_weights;
+  int num_rows;
+  long long sf_token_bytes;
+  void* d;
+  const int* problem_sizes;
+  const int* expert_offsets;
+  const int* blockscale_offsets;
+  int num_experts, n, k;
+  int wait_at_start;
+  uint32_t* counters;
+  int last_of_call;
+  uint32_t earlier_ctas;
+};
+
+// One CTA of shape S: `block` of `blocks` CTAs that serve the experts with min_rows <= rows <= max_rows (work counter
+// `bucket`).  The tensor maps are the kernel's __grid_constant__ parameters.
 template <typename OutT, class S>
-__global__ void __launch_bounds__(THREADS, 1)
-mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
-                        const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
-                        const __grid_constant__ CUtensorMap map_xt, const __grid_constant__ CUtensorMap map_sfx,
-                        const __grid_constant__ CUtensorMap map_sfw, const uint8_t* __restrict__ a_codes,
-                        const uint8_t* __restrict__ w_codes, const uint8_t* __restrict__ sf_tokens,
-                        const uint8_t* __restrict__ sf_weights, int num_rows, long long sf_token_bytes, int use_lsu,
-                        OutT* __restrict__ d, const int* __restrict__ problem_sizes,
-                        const int* __restrict__ expert_offsets, const int* __restrict__ blockscale_offsets,
-                        int num_experts, int n, int k, int min_rows, int max_rows, int wait_at_start,
-                        const __grid_constant__ RowScatter scatter, uint32_t* counters, int bucket, int last_of_call,
-                        uint32_t earlier_ctas) {
+__device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const CUtensorMap& map_x16,
+                                               const CUtensorMap& map_x32, const CUtensorMap& map_x64,
+                                               const CUtensorMap& map_xt, const CUtensorMap& map_sfx,
+                                               const CUtensorMap& map_sfw, const KernelArgs& args,
+                                               const RowScatter& scatter, int min_rows, int max_rows, int bucket,
+                                               int use_lsu, int block, int blocks) {
+  const uint8_t* __restrict__ a_codes = args.a_codes;
+  const uint8_t* __restrict__ w_codes = args.w_codes;
+  const uint8_t* __restrict__ sf_tokens = args.sf_tokens;
+  const uint8_t* __restrict__ sf_weights = args.sf_weights;
+  const int num_rows = args.num_rows;
+  const long long sf_token_bytes = args.sf_token_bytes;
+  OutT* __restrict__ d = static_cast<OutT*>(args.d);
+  const int* __restrict__ problem_sizes = args.problem_sizes;
+  const int* __restrict__ expert_offsets = args.expert_offsets;
+  const int* __restrict__ blockscale_offsets = args.blockscale_offsets;
+  const int num_experts = args.num_experts, n = args.n, k = args.k;
+  const int wait_at_start = args.wait_at_start, last_of_call = args.last_of_call;
+  uint32_t* counters = args.counters;
+  const uint32_t earlier_ctas = args.earlier_ctas;
   constexpr int TOK_TILE = S::TOK_TILE, STAGES = S::STAGES, X_BYTES = S::X_BYTES, STAGE_BYTES = S::STAGE_BYTES;
   constexpr int LANES = S::LANES;
   extern __shared__ uint8_t smem_raw[];
@@ -254,7 +283,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
     uint32_t ph = 0, qph = 0;
     uint32_t* counter = counters ? counters + bucket : nullptr;
     int t_mine = 0;                   // lane 0: the index that goes out next
-    if (lane == 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : (int)blockIdx.x;
+    if (lane == 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : block;
     while (true) {
       // lane 0 hands the tile index (or the end mark) to the other roles
       int t = -1;
@@ -266,7 +295,7 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
           ctl->q_tile[qs] = t;
           ptx::mbar_arrive(&ctl->q_full[qs]);
           // the next index is requested now; its round trip to L2 hides behind this tile's loads
-          if (t >= 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : t_mine + (int)gridDim.x;
+          if (t >= 0) t_mine = counter ? (int)atomicAdd(counter, 1u) : t_mine + blocks;
         }
       }
       q_ok = __shfl_sync(0xffffffffu, (int)q_ok, 0) != 0;
@@ -496,12 +525,36 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
 }
 
-// earlier_ctas: in/out — CTAs launched so far by this call; the last kernel of the call waits for that many reports
-template <typename OutT, class S>
-int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bool last_of_call, int bucket,
-           uint32_t* earlier_ctas) {
-  constexpr int TOK_TILE = S::TOK_TILE;
-  constexpr size_t SMEM_BYTES = smem_bytes<S>();
+// One launch for both streaming shapes: CTAs 0 .. first_ctas-1 run the 32-token shape on the experts with
+// 1 .. split_rows rows, the others the 112-token shape on split_rows+1 .. max_rows.  The hardware starts CTAs in index
+// order, so the second shape takes the SMs as the first runs out of tiles — what two launches chained by programmatic
+// dependent launch did, for one launch less per call (~4 us of host time, ~2 us on the GPU).  first_ctas == gridDim.x
+// or == 0 leaves a single shape.
+template <typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
+                        const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
+                        const __grid_constant__ CUtensorMap map_x112, const __grid_constant__ CUtensorMap map_sfx,
+                        const __grid_constant__ CUtensorMap map_sfw, const __grid_constant__ KernelArgs args,
+                        const __grid_constant__ RowScatter scatter, int first_ctas, int split_rows, int max_rows,
+                        int use_lsu_first, int use_lsu_second) {
+  if ((int)blockIdx.x < first_ctas)
+    grouped_mm_cta<OutT, ShapeTiny>(map_w, map_x16, map_x32, map_x64, map_x32, map_sfx, map_sfw, args, scatter, 1,
+                                    split_rows, 0, use_lsu_first, (int)blockIdx.x, first_ctas);
+  else
+    grouped_mm_cta<OutT, ShapeMid>(map_w, map_x16, map_x32, map_x64, map_x112, map_sfx, map_sfw, args, scatter,
+                                   split_rows + 1, max_rows, 1, use_lsu_second, (int)blockIdx.x - first_ctas,
+                                   (int)gridDim.x - first_ctas);
+}
+
+// earlier_ctas: in/out — CTAs launched so far by this call; the last kernel of the call waits for that many reports.
+// Experts with 1 .. tiny_max rows go to the 32-token shape (if want_tiny), tiny_max+1 .. mid_max to the 112-token shape
+// (if want_mid).
+template <typename OutT>
+int launch_streaming(const CallArgs& c, int tiny_max, int mid_max, bool want_tiny, bool want_mid, bool first_of_call,
+                     bool last_of_call, uint32_t* earlier_ctas) {
+  constexpr size_t SMEM_TINY = smem_bytes<ShapeTiny>(), SMEM_MID = smem_bytes<ShapeMid>();
+  constexpr size_t SMEM_BYTES = SMEM_TINY > SMEM_MID ? SMEM_TINY : SMEM_MID;
   DeviceInfo info;
   int rc = get_device_info(&info);
   if (rc != ES_B200_OK) return rc;
@@ -509,7 +562,8 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
   CUtensorMap map_w, map_x[4];
   rc = make_tensormap_u8_sw128(&map_w, c.b, (uint64_t)c.num_experts * c.n, (uint64_t)c.k, TILE_N);
   if (rc != ES_B200_OK) return rc;
-  const uint32_t boxes[4] = {16, 32, 64, (uint32_t)TOK_TILE};   // token boxes; the last one is the shape's full tile
+  const uint32_t boxes[4] = {16, 32, 64, (uint32_t)ShapeMid::TOK_TILE};   // token boxes; 32 and 112 are the full tiles
+  static_assert(ShapeTiny::TOK_TILE == 32, "the 32-row token box doubles as the small shape's full tile");
   for (int i = 0; i < 4; ++i) {
     rc = make_tensormap_u8_sw128(&map_x[i], c.a, (uint64_t)c.num_rows, (uint64_t)c.k, boxes[i]);
     if (rc != ES_B200_OK) return rc;
@@ -524,7 +578,7 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
   rc = make_tensormap_records512(&map_sfx, c.sfa, sfx_records ? sfx_records : 1);
   if (rc != ES_B200_OK) return rc;
 
-  auto kernel = mxfp8_grouped_mm_kernel<OutT, S>;
+  auto kernel = mxfp8_grouped_mm_kernel<OutT>;
   static bool configured[64] = {false};   // per device (one static per instantiation)
   int dev = 0;
   ES_CUDA_TRY(cudaGetDevice(&dev));
@@ -534,9 +588,11 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
   }
   // upper bound of the tile count known on the host: one token tile per expert
   const int64_t max_tiles = (int64_t)c.num_experts * (c.n / TILE_N);
-  int grid = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
+  int per_shape = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
   const int cap = tunables().mm_stream_max_ctas;
-  if (cap > 0 && grid > cap) grid = cap;
+  if (cap > 0 && per_shape > cap) per_shape = cap;
+  const int first_ctas = want_tiny ? per_shape : 0;
+  const int grid = first_ctas + (want_mid ? per_shape : 0);
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -548,13 +604,13 @@ int launch(const CallArgs& c, int min_rows, int max_rows, bool first_of_call, bo
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const int use_lsu = (S::SECOND_LOAD_PATH && tunables().mm_stream_lsu) ? 1 : 0;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], map_sfx, map_sfw,
-                                 static_cast<const uint8_t*>(c.a), static_cast<const uint8_t*>(c.b), c.sfa, c.sfb,
-                                 (int)c.num_rows, (long long)(c.sfa_rows * (c.k / 32)), use_lsu,
-                                 static_cast<OutT*>(c.d), c.ps, c.eo, c.bo, c.num_experts, c.n, c.k, min_rows, max_rows,
-                                 first_of_call ? 1 : 0, *c.scatter, c.counters, bucket, last_of_call ? 1 : 0,
-                                 *earlier_ctas));
+  const int lsu = tunables().mm_stream_lsu ? 1 : 0;
+  KernelArgs args = {static_cast<const uint8_t*>(c.a), static_cast<const uint8_t*>(c.b), c.sfa, c.sfb, (int)c.num_rows,
+                     (long long)(c.sfa_rows * (c.k / 32)), c.d, c.ps, c.eo, c.bo, c.num_experts, c.n, c.k,
+                     first_of_call ? 1 : 0, c.counters, last_of_call ? 1 : 0, *earlier_ctas};
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], map_sfx, map_sfw, args,
+                                 *c.scatter, first_ctas, tiny_max, mid_max,
+                                 (ShapeTiny::SECOND_LOAD_PATH && lsu) ? 1 : 0, (ShapeMid::SECOND_LOAD_PATH && lsu) ? 1 : 0));
   *earlier_ctas += (uint32_t)grid;
   return ES_B200_OK;
 }
@@ -652,17 +708,10 @@ static int grouped_mm_impl(const void* a, const void* b, const uint8_t* sfa, con
     rc = pair(tn.mm_pair_first_clusters, false);
     if (rc != ES_B200_OK) return rc;
   }
-  if (want_tiny) {
-    const bool last = !want_mid && !want_pair;
-    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeTiny>(c, 1, tiny_max, first, last, 0, &ctas)
-              : mm::launch<__half, mm::ShapeTiny>(c, 1, tiny_max, first, last, 0, &ctas);
-    if (rc != ES_B200_OK) return rc;
-    first = false;
-  }
-  if (want_mid) {
+  if (want_tiny || want_mid) {
     const bool last = !want_pair;
-    rc = bf16 ? mm::launch<__nv_bfloat16, mm::ShapeMid>(c, tiny_max + 1, heavy_min - 1, first, last, 1, &ctas)
-              : mm::launch<__half, mm::ShapeMid>(c, tiny_max + 1, heavy_min - 1, first, last, 1, &ctas);
+    rc = bf16 ? mm::launch_streaming<__nv_bfloat16>(c, tiny_max, heavy_min - 1, want_tiny, want_mid, first, last, &ctas)
+              : mm::launch_streaming<__half>(c, tiny_max, heavy_min - 1, want_tiny, want_mid, first, last, &ctas);
     if (rc != ES_B200_OK) return rc;
     first = false;
   }
