@@ -6,9 +6,9 @@
 
 For every workload and step count the two implementations run INTERLEAVED (ours, reference, ours, reference, ...),
 `repeats` timed groups of `steps` calls each (CUDA events on the launching stream, after warm-up); the SM clock is
-sampled with nvidia-smi while each arm runs (groups of 100 calls or more).  One JSON line per measurement: medians of ms per call for both arms,
-their ratio, ms x median SM MHz (what the call costs in SM cycles, comparable across power-cap states) and the output
-agreement.  Never run on more than one GPU: the reference kernel issues cluster-multicast TMA loads.
+sampled with nvidia-smi while each arm runs (groups of 100 calls or more).  One JSON line per measurement: medians of
+ms per call for both arms, their ratio, ms x median SM MHz (what the call costs in SM cycles, comparable across
+power-cap states) and the output agreement.  Never run on more than one GPU: the reference kernel issues cluster-multicast TMA loads.
 """
 from __future__ import annotations
 

@@ -44,6 +44,9 @@ def test_blockwise_matches_oracle(counts, N, K, out_dtype):
     (33, 64, 96, 1024, 512),      # 33..64 rows: tiles of 4 K blocks = one pass over the TMEM partials
     (65, 200, 40, 1024, 1152),    # >= 65 rows, some experts with two token tiles
     (1, 150, 120, 896, 384),      # all three buckets in one call
+    (1, 40, 150, 640, 256),       # two K blocks: work items of four weight tiles, 5 tiles per expert (4 + 1)
+    (1, 100, 100, 1408, 512),     # four K blocks: items of two weight tiles, 11 tiles per expert (5 x 2 + 1)
+    (1, 32, 200, 7168, 256),      # the short-K point of the reference's benchmark at test size
 ])
 def test_blockwise_many_tiles_per_cta(lo, hi, E, N, K):
     """More tiles than SMs, so that every CTA walks several tiles: covers the hand-over between the two epilogue
