@@ -525,26 +525,30 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
   end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
 }
 
-// One launch for both streaming shapes: CTAs 0 .. first_ctas-1 run the 32-token shape on the experts with
-// 1 .. split_rows rows, the others the 112-token shape on split_rows+1 .. max_rows.  The hardware starts CTAs in index
+// One launch for both streaming shapes: tiny_ctas CTAs run the 32-token shape on the experts with 1 .. split_rows rows,
+// the others the 112-token shape on split_rows+1 .. max_rows.  The hardware starts CTAs in index
 // order, so the second shape takes the SMs as the first runs out of tiles — what two launches chained by programmatic
-// dependent launch did, for one launch less per call (~4 us of host time, ~2 us on the GPU).  first_ctas == gridDim.x
-// or == 0 leaves a single shape.
+// dependent launch did, for one launch less per call (~4 us of host time).  tiny_ctas == gridDim.x or == 0 leaves a
+// single shape.
 template <typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
                         const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
                         const __grid_constant__ CUtensorMap map_x112, const __grid_constant__ CUtensorMap map_sfx,
                         const __grid_constant__ CUtensorMap map_sfw, const __grid_constant__ KernelArgs args,
-                        const __grid_constant__ RowScatter scatter, int first_ctas, int split_rows, int max_rows,
-                        int use_lsu_first, int use_lsu_second) {
-  if ((int)blockIdx.x < first_ctas)
+                        const __grid_constant__ RowScatter scatter, int tiny_ctas, int mid_first, int split_rows,
+                        int max_rows, int use_lsu_tiny, int use_lsu_mid) {
+  // CTAs [0, tiny_ctas) run the 32-token shape and the rest the 112-token shape, or the other way round (mid_first)
+  const int mid_ctas = (int)gridDim.x - tiny_ctas;
+  const int first_ctas = mid_first ? mid_ctas : tiny_ctas;
+  const bool in_first = (int)blockIdx.x < first_ctas;
+  const int block = in_first ? (int)blockIdx.x : (int)blockIdx.x - first_ctas;
+  if (in_first != (mid_first != 0))
     grouped_mm_cta<OutT, ShapeTiny>(map_w, map_x16, map_x32, map_x64, map_x32, map_sfx, map_sfw, args, scatter, 1,
-                                    split_rows, 0, use_lsu_first, (int)blockIdx.x, first_ctas);
+                                    split_rows, 0, use_lsu_tiny, block, tiny_ctas);
   else
     grouped_mm_cta<OutT, ShapeMid>(map_w, map_x16, map_x32, map_x64, map_x112, map_sfx, map_sfw, args, scatter,
-                                   split_rows + 1, max_rows, 1, use_lsu_second, (int)blockIdx.x - first_ctas,
-                                   (int)gridDim.x - first_ctas);
+                                   split_rows + 1, max_rows, 1, use_lsu_mid, block, mid_ctas);
 }
 
 // earlier_ctas: in/out — CTAs launched so far by this call; the last kernel of the call waits for that many reports.
@@ -609,7 +613,7 @@ int launch_streaming(const CallArgs& c, int tiny_max, int mid_max, bool want_tin
                      (long long)(c.sfa_rows * (c.k / 32)), c.d, c.ps, c.eo, c.bo, c.num_experts, c.n, c.k,
                      first_of_call ? 1 : 0, c.counters, last_of_call ? 1 : 0, *earlier_ctas};
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], map_sfx, map_sfw, args,
-                                 *c.scatter, first_ctas, tiny_max, mid_max,
+                                 *c.scatter, first_ctas, tunables().mm_stream_mid_first ? 1 : 0, tiny_max, mid_max,
                                  (ShapeTiny::SECOND_LOAD_PATH && lsu) ? 1 : 0, (ShapeMid::SECOND_LOAD_PATH && lsu) ? 1 : 0));
   *earlier_ctas += (uint32_t)grid;
   return ES_B200_OK;

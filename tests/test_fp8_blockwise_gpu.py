@@ -59,6 +59,15 @@ def test_blockwise_many_tiles_per_cta(lo, hi, E, N, K):
     _check(inp, d, torch.bfloat16)
 
 
+def test_blockwise_more_experts_than_the_shared_memory_tables_hold():
+    """400 experts: the per-expert tables behind the item prefix hold the first 312; the rest come from global memory."""
+    counts = [(5 * e) % 37 for e in range(400)]
+    counts[2], counts[350], counts[399] = 140, 90, 50
+    inp = C.fp8_blockwise_inputs(counts, 256, 256, seed=8)
+    d = C.run_fp8_blockwise_op(inp)
+    _check(inp, d, torch.bfloat16)
+
+
 def test_blockwise_reference_test_shapes():
     """The reference's own test draws n, k in 128*[1,64], m in [1,256], E in {8..128}; one seeded draw of that family."""
     import random

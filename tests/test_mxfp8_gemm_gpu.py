@@ -65,6 +65,16 @@ def test_mm_many_small_experts():
     _check_against_oracle(inp, d, torch.bfloat16)
 
 
+def test_mm_more_experts_than_the_shared_memory_tables_hold():
+    """Beyond 256 experts only part of the per-expert tables fits behind the item prefix in shared memory (300 experts:
+    the first 241); the others are read from global memory.  All three buckets have experts on both sides."""
+    counts = [(7 * e) % 41 for e in range(300)]
+    counts[3], counts[250], counts[280], counts[299] = 200, 150, 70, 33
+    inp = C.mxfp8_gemm_inputs(counts, 256, 256, seed=21)
+    d = C.run_mxfp8_mm_op(inp)
+    _check_against_oracle(inp, d, torch.bfloat16)
+
+
 def test_mm_does_not_write_outside_experts():
     counts = [3, 20]
     inp = C.mxfp8_gemm_inputs(counts, 128, 128, seed=9)
@@ -99,3 +109,54 @@ def test_mm_matches_reference_kernel_fixture(name):
     frac = float((d.view(torch.int16) != ref.view(torch.int16)).float().mean())
     assert frac < 0.05, f"{frac:.4f} of outputs differ from the reference kernel in the last bit"
     _check_against_oracle(inp, d, out_dtype)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("counts,N,K", [
+    ([5, 0, 130, 64, 1, 257], 256, 384),      # all three buckets; the CTA-pair kernel holds its chunks before storing
+    ([193, 385, 577, 64], 256, 256),          # two K blocks: the CTA-pair kernel stores each chunk as it is read
+    ([1000, 20], 128, 128),                   # one K block, odd number of weight tiles
+    ([400, 33, 7], 512, 768),
+])
+def test_scatter_epilogue_equals_dense_output(counts, N, K, out_dtype):
+    """es_b200_mxfp8_grouped_mm_scatter with a random permutation of the rows into one local buffer: row r of the dense
+    result must arrive, bit for bit, in row perm[r] (same kernels, same arithmetic, only the epilogue's destination
+    differs); rows of the buffer that no output row maps to stay untouched."""
+    import ctypes
+    from expert_specialization_moe_b200 import _cabi
+    inp = C.mxfp8_gemm_inputs(counts, N, K, seed=3)
+    dense = C.run_mxfp8_mm_op(inp, out_dtype)
+    dev = torch.device("cuda")
+    E = len(counts)
+    T = inp["a_codes"].shape[0]
+    slots = T + 5
+    a = torch.from_numpy(inp["a_codes"]).to(dev)
+    w = torch.from_numpy(inp["w_codes"]).to(dev)
+    sfa = torch.from_numpy(inp["sfa"]).to(dev)
+    sfb = torch.from_numpy(inp["sfb"]).to(dev)
+    ps, eo, bo = (torch.from_numpy(inp[k]).to(dev) for k in ("ps", "eo", "bo"))
+    g = torch.Generator(device="cpu")
+    g.manual_seed(7)
+    perm = torch.randperm(slots, generator=g)[:T].to(torch.int32)
+    meta = torch.stack([torch.zeros_like(perm), perm], dim=1).contiguous().to(dev)
+    out = torch.full((slots, N), 7.0, dtype=out_dtype, device=dev)
+    table = (ctypes.c_void_p * 1)(out.data_ptr())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    scratch = _cabi.grouped_mm_scratch(dev, stream)
+    dt = _cabi.BF16 if out_dtype == torch.bfloat16 else _cabi.FP16
+    _cabi.check(_cabi.load().es_b200_mxfp8_grouped_mm_scatter(
+        a.data_ptr(), w.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), dt, ps.data_ptr(), eo.data_ptr(), bo.data_ptr(),
+        E, T, N, K, sfa.numel() // (K // 32), meta.data_ptr(), table, 1, slots, scratch.data_ptr(), scratch.numel(),
+        stream))
+    torch.cuda.synchronize()
+    rc, raw = C.device_status()
+    assert rc == 0, f"device status {raw:#x}"
+    out = out.cpu()
+    valid = torch.zeros(T, dtype=torch.bool)
+    for e, m in enumerate(counts):
+        valid[int(inp["eo"][e]):int(inp["eo"][e]) + m] = True
+    rows = perm.long()[valid]
+    assert torch.equal(out[rows].view(torch.int16), dense[valid].view(torch.int16))
+    untouched = torch.ones(slots, dtype=torch.bool)
+    untouched[rows] = False
+    assert bool((out[untouched] == 7.0).all())
