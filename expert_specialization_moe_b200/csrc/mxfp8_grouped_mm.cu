@@ -662,19 +662,20 @@ static int grouped_mm_impl(const void* a, const void* b, const uint8_t* sfa, con
     ES_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "scratch must be 16-byte aligned");
   }
   // Tile-shape specialisation.  Problem sizes live on the device, so the host cannot bucket the experts; instead
-  // one kernel per row-count bucket is launched, back to back on the caller's stream with programmatic dependent
-  // launch, and each one filters the experts by row count inside its own work-list scan:
+  // the kernels of all row-count buckets are launched, back to back on the caller's stream with programmatic
+  // dependent launch (the two single-CTA shapes share one launch), and each CTA filters the experts by row count
+  // inside its own work-list scan:
   //   rows <= tiny_max  : single-CTA kernel, 128 weights x <=32 tokens, 10-slot ring   \  these experts stream their
   //   rows <  heavy_min : single-CTA kernel, 128 weights x <=112 tokens, 6-slot ring   /  weights from HBM exactly
   //                       once; what counts is weight bytes per second and SM;
   //   rows >= heavy_min : CTA-pair kernel, 256 weights x <=384 tokens, weight-stationary K step — these experts
   //                       re-read operands from L2, what counts is operand bytes per FLOP.
-  // A kernel whose bucket is empty exits after its scan.  A bucket that even the host-known upper bound of rows per
-  // expert (num_rows) cannot reach is not launched at all.  The thresholds come from a per-(n, k) table
+  // A CTA whose bucket is empty ends after its scan.  A bucket that even the host-known upper bound of rows per
+  // expert (num_rows) cannot reach gets no CTAs at all.  The thresholds come from a per-(n, k) table
   // (bucket_table.cuh) unless a tunable overrides them.
   //
   // With scratch (work counters) a large call is SPLIT: a pair launch capped to a few CTA pairs goes first, then the
-  // two streaming kernels on the SMs it leaves, then a second pair launch that takes the SMs the streaming kernels
+  // streaming launch on the SMs it leaves, then a second pair launch that takes the SMs the streaming kernels
   // free and drains the same counter.  The streaming buckets are bound by HBM and leave the tensor pipe idle, the pair
   // bucket is bound by the tensor pipe and leaves HBM idle: side by side the call costs about max() of the two
   // instead of their sum.  Every kernel is persistent and takes tiles from its bucket's counter, and no kernel of the
