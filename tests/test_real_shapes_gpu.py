@@ -203,6 +203,21 @@ def test_split_and_unsplit_calls_agree(gate_up):
     assert rc == 0, f"device status {raw:#x}"
 
 
+def test_order_of_the_streaming_shapes_does_not_change_the_output(gate_up):
+    """The two single-CTA shapes share one launch; which of them gets the lower CTA indices is a tunable and must not
+    change a bit of the result."""
+    from expert_specialization_moe_b200 import _cabi
+    d_default = _run(gate_up, torch.bfloat16)
+    _cabi.set_tunable("mm_stream_mid_first", 1)
+    try:
+        d_swapped = _run(gate_up, torch.bfloat16)
+    finally:
+        _cabi.set_tunable("mm_stream_mid_first", 0)
+    assert torch.equal(d_default, d_swapped)
+    rc, raw = C.device_status()
+    assert rc == 0, f"device status {raw:#x}"
+
+
 def test_c_abi_call_with_caller_scratch_leaves_the_work_counters_zeroed(gate_up):
     """Straight through the C ABI with the caller's own scratch: same output as the torch operator, and the scratch
     is all zero again after every call (which is what lets one buffer serve every call on a stream)."""
