@@ -53,3 +53,43 @@ def test_quant_then_gemm_replays_from_a_cuda_graph():
     assert torch.equal(replayed, d) and not torch.equal(replayed, eager)
     rc, raw = C.device_status()
     assert rc == 0, raw
+
+
+def test_calls_on_two_streams_at_once_keep_their_work_counters_apart():
+    """Every stream that runs grouped GEMM calls has its own 256 bytes of work counters (the torch operator keeps one
+    buffer per device and stream).  Two streams issue calls of different problem lists back to back, with no
+    synchronisation between them; each stream's outputs must equal what the same calls give one after the other."""
+    from expert_specialization_moe_b200 import es_sm100_mxfp8_blockscaled_grouped_mm as mm
+    dev = "cuda"
+    cases = []
+    for counts, N, K, seed in [([200, 5, 0, 40, 3000, 17], 512, 512, 1), ([31] * 40 + [2500], 256, 768, 2)]:
+        inp = C.mxfp8_gemm_inputs(counts, N, K, seed=seed)
+        T = inp["a_codes"].shape[0]
+        t = {k: torch.from_numpy(inp[k]).to(dev) for k in ("a_codes", "w_codes", "sfa", "sfb", "ps", "eo", "bo")}
+        cases.append(dict(a=t["a_codes"].view(torch.float8_e4m3fn),
+                          b=t["w_codes"].view(torch.float8_e4m3fn).transpose(1, 2), sfa=t["sfa"], sfb=t["sfb"],
+                          ps=t["ps"], eo=t["eo"], bo=t["bo"], T=T, N=N))
+
+    def call(c, d):
+        mm(d, c["a"], c["b"], c["sfa"], c["sfb"], c["ps"], c["eo"], c["bo"])
+
+    serial = []
+    for c in cases:
+        d = torch.zeros((c["T"], c["N"]), dtype=torch.bfloat16, device=dev)
+        call(c, d)
+        torch.cuda.synchronize()
+        serial.append(d)
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [[torch.zeros_like(serial[i]) for _ in range(6)] for i in range(2)]
+    for s in streams:
+        s.wait_stream(torch.cuda.current_stream())
+    for rep in range(6):
+        for i, s in enumerate(streams):
+            with torch.cuda.stream(s):
+                call(cases[i], outs[i][rep])
+    torch.cuda.synchronize()
+    for i in range(2):
+        for rep in range(6):
+            assert torch.equal(outs[i][rep], serial[i]), f"stream {i}, call {rep}"
+    rc, raw = C.device_status()
+    assert rc == 0, raw
