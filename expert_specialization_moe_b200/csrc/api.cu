@@ -62,7 +62,7 @@ Tunables& tunables() {
       env_or("ES_B200_MM_PAIR_FIRST_CLUSTERS", 32), env_or("ES_B200_MM_SPLIT_MIN_ROWS", 2048),
       env_or("ES_B200_MM_STREAM_MAX_CTAS", 0),     env_or("ES_B200_MM_PAIR_MAX_CLUSTERS", 0),
       env_or("ES_B200_MM_DYNAMIC", 1),             env_or("ES_B200_MM_STREAM_LSU", 1),
-      env_or("ES_B200_MM_STREAM_MID_FIRST", 0),
+      env_or("ES_B200_MM_STREAM_MID_LEAD_CTAS", -1),
   };
   return t;
 }
@@ -78,7 +78,7 @@ extern "C" int es_b200_set_tunable(const char* name, int value) {
       {"mm_pair_first_clusters", &t.mm_pair_first_clusters}, {"mm_split_min_rows", &t.mm_split_min_rows},
       {"mm_stream_max_ctas", &t.mm_stream_max_ctas},       {"mm_pair_max_clusters", &t.mm_pair_max_clusters},
       {"mm_dynamic", &t.mm_dynamic},                       {"mm_stream_lsu", &t.mm_stream_lsu},
-      {"mm_stream_mid_first", &t.mm_stream_mid_first},
+      {"mm_stream_mid_lead_ctas", &t.mm_stream_mid_lead_ctas},
   };
   for (const auto& e : table)
     if (strcmp(e.n, name) == 0) {

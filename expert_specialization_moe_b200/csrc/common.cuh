@@ -61,8 +61,9 @@ struct Tunables {
   int mm_pair_max_clusters;     // cap of the trailing pair launch (0 = as many CTA pairs as fit)
   int mm_dynamic;               // 1: tiles are dealt through the work counters in scratch when scratch is given
   int mm_stream_lsu;            // 1: the streaming kernels fill every other ring slot with cp.async instead of TMA
-  int mm_stream_mid_first;      // 1: in the streaming launch the CTAs of the 112-token shape come before those of the
-                                // 32-token shape (the larger tiles first, the smaller ones fill the tail)
+  int mm_stream_mid_lead_ctas;  // streaming launch: this many CTAs of the 112-token shape start before the 32-token
+                                // shape's (they work through the middle bucket from the start); the rest follow it;
+                                // negative = built-in default
 };
 Tunables& tunables();
 void note_device_error();   // es_b200_check_status found status bits set (see es_b200_error_epoch)

@@ -204,16 +204,18 @@ def test_split_and_unsplit_calls_agree(gate_up):
 
 
 def test_order_of_the_streaming_shapes_does_not_change_the_output(gate_up):
-    """The two single-CTA shapes share one launch; which of them gets the lower CTA indices is a tunable and must not
-    change a bit of the result."""
+    """The two single-CTA shapes share one launch; how many CTAs of the 112-token shape get the lowest CTA indices (and
+    so start first) is a tunable and must not change a bit of the result."""
     from expert_specialization_moe_b200 import _cabi
-    d_default = _run(gate_up, torch.bfloat16)
-    _cabi.set_tunable("mm_stream_mid_first", 1)
+    lib = _cabi.load()
+    outs = []
     try:
-        d_swapped = _run(gate_up, torch.bfloat16)
+        for lead in (0, 20, 100000):              # none, a few, all of them
+            _cabi.set_tunable("mm_stream_mid_lead_ctas", lead)
+            outs.append(_run(gate_up, torch.bfloat16))
     finally:
-        _cabi.set_tunable("mm_stream_mid_first", 0)
-    assert torch.equal(d_default, d_swapped)
+        lib.es_b200_set_tunable(b"mm_stream_mid_lead_ctas", -1)      # back to the built-in default (see below)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
     rc, raw = C.device_status()
     assert rc == 0, f"device status {raw:#x}"
 
