@@ -147,6 +147,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
   constexpr int TOK = S::TOK_TILE;
   constexpr int STAGES = S::STAGES;
   constexpr int NCH = S::NCH;
+  if (!wait_at_start) pdl_launch_dependents();   // not the first kernel of its call: the next one may launch at once
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* chunks = reinterpret_cast<float*>(smem + (size_t)STAGES * S::STAGE_BYTES);        // [NCH][CH_KT][TOK]
@@ -193,7 +194,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
   });
   // a launch without work (the host only knows an upper bound of the rows per expert) ends here
   if (ctl->tile_prefix[num_experts] == 0) {
-    pdl_launch_dependents();
+    if (wait_at_start) pdl_launch_dependents();
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) ptx::tmem_dealloc(ctl->tmem_base, S::TMEM_COLS);
@@ -204,7 +205,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
   ptx::tc_fence_before_sync();
   __syncthreads();
   ptx::tc_fence_after_sync();
-  pdl_launch_dependents();
+  if (wait_at_start) pdl_launch_dependents();
 
   const uint32_t tmem_base = ctl->tmem_base;
   const int total_items = ctl->tile_prefix[num_experts];

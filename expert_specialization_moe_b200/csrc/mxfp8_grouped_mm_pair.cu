@@ -160,6 +160,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
                              const int* __restrict__ blockscale_offsets, int num_experts, int n, int k, int min_rows,
                              int wait_at_start, const __grid_constant__ RowScatter scatter, uint32_t* counters,
                              int last_of_call, uint32_t earlier_ctas) {
+  if (!wait_at_start) pdl_launch_dependents();   // not the first kernel of its call: the next one may launch at once
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 16 x 512 bytes, one per epilogue warp
@@ -197,6 +198,8 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   // everything before it (griddepcontrol.wait) before it lets the others start, so the operands are final; the
   // kernels write disjoint rows of d.  A launch that is not first therefore starts on SMs as they become free; stream
   // order for whatever follows the call is kept at the end (end_of_kernel).
+  // (a launch that is not first has let the next kernel of the call launch at entry; the first one does so after its
+  // prologue, below)
   if (wait_at_start) pdl_wait_prior_grid();
   const int n_tiles = n / TILE_N;
   const int n_pairs = (n_tiles + 1) >> 1;
@@ -214,7 +217,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   // A launch without work (the host only knows an upper bound of the rows per expert) ends here, before it holds
   // TMEM or has signalled its partner CTA; both CTAs of a pair see the same total.
   if (ctl->table[num_experts] == 0) {
-    pdl_launch_dependents();
+    if (wait_at_start) pdl_launch_dependents();
     end_of_kernel(counters, wait_at_start != 0, last_of_call != 0, earlier_ctas, scatter.meta != nullptr, &g_status);
     return;
   }
@@ -227,7 +230,7 @@ mxfp8_grouped_mm_pair_kernel(const __grid_constant__ Maps maps, OutT* __restrict
   ptx::tc_fence_before_sync();
   ptx::cluster_sync();
   ptx::tc_fence_after_sync();
-  pdl_launch_dependents();
+  if (wait_at_start) pdl_launch_dependents();
 
   const uint32_t tmem_base = ctl->tmem_base;
   const int total_tiles = tab.prefix[num_experts];

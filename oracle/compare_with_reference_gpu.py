@@ -5,7 +5,8 @@
                                                 [--repeats 5] [--quant]
 
 For every workload and step count the two implementations run INTERLEAVED (ours, reference, ours, reference, ...),
-`repeats` timed groups of `steps` calls each (CUDA events on the launching stream, after warm-up); the SM clock is
+`repeats` timed groups of `steps` calls each (CUDA events on the launching stream, after warm-up; groups of fewer than
+100 calls start after 1.5 s of idle GPU: the burst regime, as `bench.py --steps 20` in a fresh process); the SM clock is
 sampled with nvidia-smi while each arm runs (groups of 100 calls or more).  One JSON line per measurement: medians of
 ms per call for both arms, their ratio, ms x median SM MHz (what the call costs in SM cycles, comparable across
 power-cap states) and the output agreement.  Never run on more than one GPU: the reference kernel issues cluster-multicast TMA loads.
@@ -34,6 +35,14 @@ def timed_group(fn, steps, dev):
         sampler.start()
         time.sleep(0.3)
         fn()
+    else:
+        # short groups measure the burst regime: a few calls of this arm (so that nothing of the other arm is in
+        # flight or in the caches), then 1.5 s of idle GPU.  Back to back with the other arm's group they would run
+        # inside the clock governor's settling time after the other kernel's different power draw.
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        time.sleep(1.5)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
