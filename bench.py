@@ -69,6 +69,15 @@ WORKLOADS = {
     "ref_dist_ep8": (32, None, 4096, 7168, "MXFP8 grouped GEMM on the reference's SM100 benchmark: DeepSeek-R1 gate_up "
                                            "EP8 decode (n=4096, k=7168, E=32), row counts 70/15/10/5 % from "
                                            "1-32/32-64/64-128/128-1024"),
+    # the other four shapes of that benchmark (same row distribution)
+    "ref_dist_down": (256, None, 7168, 256, "MXFP8 grouped GEMM on the reference's SM100 benchmark: DeepSeek-R1 down TP8 "
+                                            "(n=7168, k=256, E=256), the benchmark's row distribution"),
+    "ref_dist_qwen_gate_up": (128, None, 768, 4096, "MXFP8 grouped GEMM on the reference's SM100 benchmark: Qwen3 gate_up "
+                                                    "TP4 (n=768, k=4096, E=128), the benchmark's row distribution"),
+    "ref_dist_qwen_down": (128, None, 4096, 384, "MXFP8 grouped GEMM on the reference's SM100 benchmark: Qwen3 down TP4 "
+                                                 "(n=4096, k=384, E=128), the benchmark's row distribution"),
+    "ref_dist_ep16": (16, None, 4096, 7168, "MXFP8 grouped GEMM on the reference's SM100 benchmark: DeepSeek-R1 gate_up "
+                                            "EP16 decode (n=4096, k=7168, E=16), the benchmark's row distribution"),
     # weight-streaming probe: 128 experts of 1..32 rows, every tile streams a [128 x 7168] slab once; with
     # --tunable mm_stream_max_ctas=<n> it gives the per-SM ingest rate of the streaming kernel at n CTAs
     "stream_probe": (128, None, 4096, 7168, "weight-streaming probe: E=128 experts of 1..32 rows (uniform), N=4096, K=7168"),
@@ -932,8 +941,9 @@ def main():
 
     # one call launches the streaming kernel (both shapes in one launch), the CTA-pair kernel when the host-known row
     # count can reach its bucket (>= 113 rows at most shapes), and a leading capped CTA-pair launch when the call is split
+    # (256 rows or more)
     rows_local = int(counts.sum())
-    launches_per_step = 1 + (rows_local >= 113) + (rows_local >= 2048)
+    launches_per_step = 1 + (rows_local >= 113) + (rows_local >= 256)
     line = None
     if rank == 0:
         ms_per_step = elapsed_ms / args.steps

@@ -59,10 +59,10 @@ static int env_or(const char* name, int fallback) {
 Tunables& tunables() {
   static Tunables t = {
       env_or("ES_B200_MM_HEAVY_MIN_ROWS", 0),      env_or("ES_B200_MM_TINY_MAX_ROWS", 0),
-      env_or("ES_B200_MM_PAIR_FIRST_CLUSTERS", 32), env_or("ES_B200_MM_SPLIT_MIN_ROWS", 2048),
+      env_or("ES_B200_MM_PAIR_FIRST_CLUSTERS", 32), env_or("ES_B200_MM_SPLIT_MIN_ROWS", 256),
       env_or("ES_B200_MM_STREAM_MAX_CTAS", 0),     env_or("ES_B200_MM_PAIR_MAX_CLUSTERS", 0),
       env_or("ES_B200_MM_DYNAMIC", 1),             env_or("ES_B200_MM_STREAM_LSU", 1),
-      env_or("ES_B200_MM_STREAM_MID_LEAD_CTAS", -1),
+      env_or("ES_B200_MM_ITEM_K_STEPS", 16), env_or("ES_B200_MM_STREAM_MID_LEAD_CTAS", -1),
   };
   return t;
 }
@@ -78,7 +78,7 @@ extern "C" int es_b200_set_tunable(const char* name, int value) {
       {"mm_pair_first_clusters", &t.mm_pair_first_clusters}, {"mm_split_min_rows", &t.mm_split_min_rows},
       {"mm_stream_max_ctas", &t.mm_stream_max_ctas},       {"mm_pair_max_clusters", &t.mm_pair_max_clusters},
       {"mm_dynamic", &t.mm_dynamic},                       {"mm_stream_lsu", &t.mm_stream_lsu},
-      {"mm_stream_mid_lead_ctas", &t.mm_stream_mid_lead_ctas},
+      {"mm_item_k_steps", &t.mm_item_k_steps}, {"mm_stream_mid_lead_ctas", &t.mm_stream_mid_lead_ctas},
   };
   for (const auto& e : table)
     if (strcmp(e.n, name) == 0) {

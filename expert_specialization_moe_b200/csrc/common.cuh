@@ -61,6 +61,7 @@ struct Tunables {
   int mm_pair_max_clusters;     // cap of the trailing pair launch (0 = as many CTA pairs as fit)
   int mm_dynamic;               // 1: tiles are dealt through the work counters in scratch when scratch is given
   int mm_stream_lsu;            // 1: the streaming kernels fill every other ring slot with cp.async instead of TMA
+  int mm_item_k_steps;          // streaming kernel: a work item spans enough weight tiles for this many K steps (<= 8 tiles)
   int mm_stream_mid_lead_ctas;  // streaming launch: this many CTAs of the 112-token shape start before the 32-token
                                 // shape's (they work through the middle bucket from the start); the rest follow it;
                                 // negative = built-in default

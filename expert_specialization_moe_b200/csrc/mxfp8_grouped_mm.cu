@@ -124,17 +124,25 @@ constexpr size_t smem_bytes() {
 __device__ uint32_t g_status = 0;   // sticky error bits of the grouped GEMM kernels (bounded waits that gave up)
 
 struct TileInfo {
-  int e, nt;
+  int e, nt;     // expert, first weight tile of the work item
+  int n_sub;     // weight tiles of the item (1 .. group)
   int valid;     // token rows of the expert (= of this tile)
   int n_mma;     // valid rounded up to 16
   int row0;      // first token row in a / d
 };
 
-// tile t of this launch -> (expert, weight tile); one token tile per expert
-__device__ __forceinline__ TileInfo decode_tile(int t, const ExpertTable& tab, int num_experts) {
+// Work item t of this launch -> (expert, its weight tiles nt .. nt + n_sub - 1); one token tile per expert.  An item
+// is `group` consecutive weight tiles (the last item of an expert may be shorter): with few K steps per tile — k = 256
+// is two — every role would otherwise spend more time on the queue hand-over and the decode of a tile than on the
+// tile, so the host sizes the items to ~16 K steps, at most 8 tiles (group = 1 from k = 2048 up).  Measured on the
+// reference benchmark's row distribution: n = 7168, k = 256, E = 256: 0.257 ms with one tile per item, 0.206 with 4,
+// 0.201 with 8; n = 4096, k = 384, E = 128: 0.103 / 0.087 / 0.085.
+__device__ __forceinline__ TileInfo decode_tile(int t, const ExpertTable& tab, int num_experts, int n_tiles, int group) {
   TileInfo ti;
   ti.e = upper_bound_expert(tab.prefix, num_experts, t);
-  ti.nt = t - tab.prefix[ti.e];
+  ti.nt = (t - tab.prefix[ti.e]) * group;
+  const int rest = n_tiles - ti.nt;
+  ti.n_sub = rest < group ? rest : group;
   ti.valid = tab.m(ti.e);
   ti.n_mma = (ti.valid + 15) & ~15;
   ti.row0 = tab.row0(ti.e);
@@ -177,6 +185,7 @@ struct KernelArgs {
   const int* blockscale_offsets;
   int num_experts, n, k;
   int wait_at_start;
+  int group;                 // weight tiles per work item
   uint32_t* counters;
   int last_of_call;
   uint32_t earlier_ctas;
@@ -201,7 +210,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
   const int* __restrict__ problem_sizes = args.problem_sizes;
   const int* __restrict__ expert_offsets = args.expert_offsets;
   const int* __restrict__ blockscale_offsets = args.blockscale_offsets;
-  const int num_experts = args.num_experts, n = args.n, k = args.k;
+  const int num_experts = args.num_experts, n = args.n, k = args.k, group = args.group;
   const int wait_at_start = args.wait_at_start, last_of_call = args.last_of_call;
   // A kernel that is not the first of its call lets the next one launch at once (measured: 1.6 % on a 0.19 ms call,
   // nothing elsewhere); the first one triggers only after its prologue — triggering right after its wait made the
@@ -262,7 +271,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
       atomicOr(&g_status, ERR_SCALE_OFFSET_BIT);
       return 0;
     }
-    return n_tiles;
+    return (n_tiles + group - 1) / group;
   });
   // A launch without work (the host only knows an upper bound of the rows per expert) ends here: the kernels of a call
   // run one after the other on every SM, and an empty one that ran its roles through the empty queue cost ~5 us of
@@ -319,7 +328,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
         break;
       }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, tab, num_experts);
+      const TileInfo ti = decode_tile(t, tab, num_experts, n_tiles, group);
       const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_xt;
       const uint32_t box_rows = ti.n_mma <= 16 ? 16u : ti.n_mma <= 32 ? 32u : ti.n_mma <= 64 ? 64u : (uint32_t)TOK_TILE;
       const uint32_t tx = W_BYTES + box_rows * TILE_K + 2 * SF_BYTES;
@@ -330,9 +339,12 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
       const CUtensorMap* my_map = lane == 0 ? &map_w : lane == 1 ? xm : lane == 2 ? &map_sfw : &map_sfx;
       const uint32_t my_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)W_BYTES
                               : lane == 2 ? (uint32_t)(W_BYTES + X_BYTES) : (uint32_t)(W_BYTES + X_BYTES + SF_BYTES);
-      const int my_c1 = lane == 0 ? ti.e * n + ti.nt * TILE_N : lane == 1 ? ti.row0 : lane == 2 ? sfw_atom : sfx_atom;
+      const int my_c1_first = lane == 0 ? ti.e * n + ti.nt * TILE_N : lane == 1 ? ti.row0 : lane == 2 ? sfw_atom : sfx_atom;
+      const int my_c1_step = lane == 0 ? TILE_N : lane == 2 ? kt_count : 0;     // per weight tile of the item
       const uint64_t my_hint = lane == 0 ? ptx::kL2EvictFirst : lane == 1 ? ptx::kL2EvictLast : ptx::kL2EvictNormal;
       bool ok = true;
+      for (int sub = 0; ok && sub < ti.n_sub; ++sub) {
+      const int my_c1 = my_c1_first + sub * my_c1_step;
       for (int kt = 0; kt < kt_count; ++kt) {
         if (!(use_lsu && (s & 1))) {          // odd slots belong to the cp.async loaders
           ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag));
@@ -346,6 +358,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
         }
         if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
+      }   // weight tiles of the item
       if (!ok) {
         if (lane == 0) {
           *abort_flag = 1;
@@ -368,7 +381,8 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
         int t;
         if (!q.next<false>(ctl, abort_flag, lane, &t)) { ok = false; break; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, tab, num_experts);
+        const TileInfo ti = decode_tile(t, tab, num_experts, n_tiles, group);
+        for (int sub = 0; ok && sub < ti.n_sub; ++sub) {
         if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_ph ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * S::ACC_COLS + mma_lane * TOK_TILE;
@@ -395,6 +409,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
         ptx::tc_commit(&ctl->tmem_full[acc]);     // this lane's share of the accumulator is complete
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
+        }   // weight tiles of the item
       }
       if (!ok) {
         *abort_flag = 1;
@@ -415,7 +430,8 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
         int t;
         if (!q.next<false>(ctl, abort_flag, lane, &t)) { ok = false; break; }
         if (t < 0) break;
-        for (int kt = 0; kt < kt_count; ++kt) {
+        const int k_steps = decode_tile(t, tab, num_experts, n_tiles, group).n_sub * kt_count;
+        for (int kk = 0; kk < k_steps; ++kk) {
           if (!ptx::mbar_wait(&ctl->full[s], ph, abort_flag)) { ok = false; break; }
           if (use_lsu && (s & 1)) ptx::fence_proxy_async_shared();
           ptx::tc_fence_after_sync();
@@ -449,7 +465,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
         int t;
         if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
         if (t < 0) break;
-        const TileInfo ti = decode_tile(t, tab, num_experts);
+        const TileInfo ti = decode_tile(t, tab, num_experts, n_tiles, group);
         const uint8_t* w_src = w_codes + ((int64_t)ti.e * n + ti.nt * TILE_N + r0) * k + c16 * 16;
         const uint8_t* x_src = a_codes + ((int64_t)ti.row0 + r0) * k + c16 * 16;
         const int64_t sfw_off = ((int64_t)(ti.e * n_tiles + ti.nt) * kt_count) * SF_BYTES;
@@ -458,6 +474,9 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
         const uint8_t* sf_src = lt < 32 ? sf_weights + sfw_off + lt * 16 : sf_tokens + sfx_off + (lt - 32) * 16;
         const bool sf_in_range = lt < 32 || sfx_off + (int64_t)kt_count * SF_BYTES <= sf_token_bytes;
         const uint32_t dst_swz = (uint32_t)(r0 * 128 + ((c16 ^ (r0 & 7)) << 4));   // row r0 + 16 j keeps (r & 7)
+        for (int sub = 0; ok && sub < ti.n_sub; ++sub) {
+        const uint8_t* w_sub = w_src + (int64_t)sub * TILE_N * k;                 // weight tile nt + sub
+        const uint8_t* sf_sub = lt < 32 ? sf_src + (int64_t)sub * kt_count * SF_BYTES : sf_src;
         for (int kt = 0; kt < kt_count; ++kt) {
           if (s & 1) {
             ok = __all_sync(0xffffffffu, ptx::mbar_wait(&ctl->empty[s], ph ^ 1u, abort_flag));
@@ -465,7 +484,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
             const uint32_t stage = ptx::smem_u32(smem + (size_t)s * STAGE_BYTES);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              ptx::cp_async_16_hint(stage + dst_swz + j * 2048, w_src + (int64_t)j * 16 * k + kt * TILE_K,
+              ptx::cp_async_16_hint(stage + dst_swz + j * 2048, w_sub + (int64_t)j * 16 * k + kt * TILE_K,
                                     ptx::kL2EvictFirst);      // weights are read once
 #pragma unroll
             for (int j = 0; j < TOK_TILE / 16; ++j) {
@@ -478,11 +497,12 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
             }
             if (lt < 64)
               ptx::cp_async_16(stage + W_BYTES + X_BYTES + lt * 16,
-                               sf_in_range ? sf_src + (int64_t)kt * SF_BYTES : sf_weights, sf_in_range ? 16u : 0u);
+                               sf_in_range ? sf_sub + (int64_t)kt * SF_BYTES : sf_weights, sf_in_range ? 16u : 0u);
             ptx::cp_async_arrive_noinc(&ctl->full[s]);
           }
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
+        }   // weight tiles of the item
       }
       if (!ok && lane == 0) {
         *abort_flag = 1;
@@ -500,12 +520,14 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
       int t;
       if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
       if (t < 0) break;
-      const TileInfo ti = decode_tile(t, tab, num_experts);
+      const TileInfo ti = decode_tile(t, tab, num_experts, n_tiles, group);
+      for (int sub = 0; ok && sub < ti.n_sub; ++sub) {
+      const int nt = ti.nt + sub;
       const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * S::ACC_COLS + ((uint32_t)(quad * 32) << 16);
-      OutT* dst = d + (int64_t)ti.row0 * n + (ti.nt * TILE_N + quad * 32);
+      OutT* dst = d + (int64_t)ti.row0 * n + (nt * TILE_N + quad * 32);
       drain_partial_sums<OutT, LANES>(
           taddr, TOK_TILE, kt_count < LANES ? kt_count : LANES, ti.n_mma, ti.valid,
           reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, dst, n, lane,
@@ -515,9 +537,10 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
           },
-          scatter, ti.row0, ti.nt * TILE_N + quad * 32, &g_status);
+          scatter, ti.row0, nt * TILE_N + quad * 32, &g_status);
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
+      }   // weight tiles of the item
     }
     if (!ok && lane == 0) {
       *abort_flag = 1;
@@ -599,8 +622,13 @@ int launch_streaming(const CallArgs& c, int tiny_max, int mid_max, bool want_tin
     ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     configured[dev & 63] = true;
   }
-  // upper bound of the tile count known on the host: one token tile per expert
-  const int64_t max_tiles = (int64_t)c.num_experts * (c.n / TILE_N);
+  // weight tiles per work item: ~mm_item_k_steps K steps per item
+  int item_k_steps = tunables().mm_item_k_steps;
+  if (item_k_steps < 1) item_k_steps = 1;
+  int group = (item_k_steps + kt_count - 1) / kt_count;
+  if (group > 8) group = 8;
+  // upper bound of the item count known on the host: one token tile per expert
+  const int64_t max_tiles = (int64_t)c.num_experts * ((c.n / TILE_N + group - 1) / group);
   int per_shape = (int)(max_tiles < info.sm_count ? max_tiles : info.sm_count);
   const int cap = tunables().mm_stream_max_ctas;
   if (cap > 0 && per_shape > cap) per_shape = cap;
@@ -624,7 +652,7 @@ int launch_streaming(const CallArgs& c, int tiny_max, int mid_max, bool want_tin
   const int lsu = tunables().mm_stream_lsu ? 1 : 0;
   KernelArgs args = {static_cast<const uint8_t*>(c.a), static_cast<const uint8_t*>(c.b), c.sfa, c.sfb, (int)c.num_rows,
                      (long long)(c.sfa_rows * (c.k / 32)), c.d, c.ps, c.eo, c.bo, c.num_experts, c.n, c.k,
-                     first_of_call ? 1 : 0, c.counters, last_of_call ? 1 : 0, *earlier_ctas};
+                     first_of_call ? 1 : 0, group, c.counters, last_of_call ? 1 : 0, *earlier_ctas};
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], map_sfx, map_sfw, args,
                                  *c.scatter, first_ctas, mid_lead, tiny_max, mid_max,
                                  (ShapeTiny::SECOND_LOAD_PATH && lsu) ? 1 : 0, (ShapeMid::SECOND_LOAD_PATH && lsu) ? 1 : 0));

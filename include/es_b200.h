@@ -236,7 +236,10 @@ int es_b200_ep_route_count_static(const void* topk_ids, int ids_are_int64, int p
  * ES_B200_<NAME IN CAPITALS>.  Names: "mm_heavy_min_rows" (experts with at least this many rows use CTA-pair tiles;
  * 0 = per-(n, k) table; at most 113), "mm_tiny_max_rows" (0 = table), "mm_pair_first_clusters",
  * "mm_split_min_rows", "mm_stream_max_ctas", "mm_pair_max_clusters" (grid shaping of a split call, 0 = no cap),
- * "mm_dynamic" (0: ignore the work counters).  Unknown name: ES_B200_ERR_INVALID_ARGUMENT.
+ * "mm_dynamic" (0: ignore the work counters), "mm_stream_lsu" (0: the streaming CTAs load by TMA only),
+ * "mm_stream_mid_lead_ctas" (CTAs of the 112-token shape that start before the 32-token shape's; negative = built-in
+ * default), "mm_item_k_steps" (K steps that a streaming work item should span: it takes that many weight tiles, at
+ * most 8).  Unknown name: ES_B200_ERR_INVALID_ARGUMENT.
  */
 int es_b200_set_tunable(const char* name, int value);
 
