@@ -87,7 +87,7 @@ template <typename OutT, int PARTS, class Release>
 __device__ __forceinline__ void drain_partial_sums(uint32_t taddr, uint32_t part_stride, int parts_written, int n_cols,
                                                    int valid, OutT* stage_warp, OutT* dst, int64_t ld, int lane,
                                                    Release release, const RowScatter& scatter, int64_t first_row,
-                                                   int col_off, uint32_t* status) {
+                                                   int col_off, uint32_t* status, bool direct_stores) {
   for (int c = 0; c < n_cols; c += 32) {
     OutT* dest = nullptr;
     if (scatter.meta != nullptr)
@@ -116,7 +116,22 @@ __device__ __forceinline__ void drain_partial_sums(uint32_t taddr, uint32_t part
       }
     }
     if (c + 32 >= n_cols) release();
-    store_chunk<OutT, 32>(acc, c, valid, stage_warp, dst, ld, lane, scatter, dest);
+    if (direct_stores && scatter.meta == nullptr) {
+      // dense output without shared memory: a warp-wide 2-byte store writes the 64 contiguous bytes of one token row.
+      // The caller asks for it when K is long (the output is a small part of the call's bytes): no store -> sync ->
+      // load round trip behind the operand traffic in shared memory (reference distribution, k = 7168 and 4096: 3-4 %
+      // per call).  With short K the output is a large part of the traffic and the staged 128-bit stores win
+      // (k = 256, n = 7168: 0.194 vs 0.222 ms; k = 384: 0.080 vs 0.089).
+      OutT* out = dst + (int64_t)c * ld + lane;
+      const int rows = valid - c;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < rows) *out = out_from_f32<OutT>(__uint_as_float(acc[j]));
+        out += ld;
+      }
+    } else {
+      store_chunk<OutT, 32>(acc, c, valid, stage_warp, dst, ld, lane, scatter, dest);
+    }
   }
 }
 
@@ -156,7 +171,8 @@ __device__ __forceinline__ void read_held_chunk(uint32_t taddr, uint32_t (&held)
 // Dense output without shared memory: a warp-wide 2-byte store writes the 64 contiguous bytes of one token row (two
 // full sectors).  The CTA-pair kernel's K loop keeps the shared-memory pipe busy (operand reads of the MMAs plus the
 // TMA fills come to ~120 of the 128 bytes per cycle) and every store -> sync -> load round trip of a staged epilogue
-// queues behind that traffic (measured: ~2900 cycles per 32 x 32 chunk staged, ~2500 direct with 8x the stores).
+// queues behind that traffic (measured: ~2900 cycles per 32 x 32 chunk staged, ~2500 direct with 8x the stores;
+// 16 x 8192-row experts at K = 768: 0.262 ms direct, 0.281 staged).
 // `out` = &d[first token of the chunk][first n of the warp]; `rows` = token rows of the chunk that exist (may be
 // <= 0 or > 32).
 __device__ __forceinline__ void store_held_chunk_dense(const uint32_t (&held)[16], uint16_t* out, int64_t ld, int rows,

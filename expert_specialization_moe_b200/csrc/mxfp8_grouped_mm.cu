@@ -537,7 +537,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
           },
-          scatter, ti.row0, nt * TILE_N + quad * 32, &g_status);
+          scatter, ti.row0, nt * TILE_N + quad * 32, &g_status, kt_count >= 8);
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
       }   // weight tiles of the item
