@@ -43,6 +43,13 @@ def test_argument_checks_happen_before_any_launch(lib):
     assert rc == 1 and b"n should align 128" in lib.es_b200_last_error()
     assert lib.es_b200_grouped_mm_scratch_bytes(8, 512, 1024, 512) == 256      # the work counters
     assert lib.es_b200_set_tunable(b"no_such_tunable", 1) == 1 and b"unknown tunable" in lib.es_b200_last_error()
+    # every name that include/es_b200.h documents is accepted (the values written are the built-in defaults)
+    for name, value in ((b"mm_heavy_min_rows", 0), (b"mm_tiny_max_rows", 0), (b"mm_pair_first_clusters", 32),
+                        (b"mm_split_min_rows", 256), (b"mm_stream_max_ctas", 0), (b"mm_pair_max_clusters", 0),
+                        (b"mm_dynamic", 1), (b"mm_stream_lsu", 1), (b"mm_stream_mid_lead_ctas", -1),
+                        (b"mm_item_k_steps", 16)):
+        assert lib.es_b200_set_tunable(name, value) == 0, name
+        assert name.decode() in (ROOT / "include" / "es_b200.h").read_text(), name
 
 
 def test_ops_mirror_reference_signatures():
