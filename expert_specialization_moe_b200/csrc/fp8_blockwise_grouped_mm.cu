@@ -100,16 +100,16 @@ struct TileInfo {
   int e, tt, nt, valid, n_mma, row0;
 };
 
-// A work item is `group` consecutive weight tiles of one (expert, token tile); a CTA takes the items blockIdx.x,
-// blockIdx.x + gridDim.x, ... and every role walks their tiles in the same order.  The item is decoded once (binary
+// A work item is `group` consecutive weight tiles of one (expert, token tile); CTA `block` of the `blocks` CTAs of its
+// shape takes the items block, block + blocks, ... and every role walks their tiles in the same order.  The item is decoded once (binary
 // search over the item prefix, a division) and the tiles inside it only advance `nt`: with two K blocks per tile
 // (k = 256) every role spent more time per tile finding out what the tile was than working on it (measured: the
 // producer lane and both MMA lanes ~2200 cycles per tile, almost none of it waiting).
 template <int TOK_TILE>
 struct TileWalk {
   TileInfo ti;
-  int item, left;
-  __device__ __forceinline__ TileWalk() : item((int)blockIdx.x - (int)gridDim.x), left(0) {}
+  int item, left, blocks;
+  __device__ __forceinline__ TileWalk(int block, int blocks_) : item(block - blocks_), left(0), blocks(blocks_) {}
   // advances to this CTA's next tile; false when there is none
   __device__ __forceinline__ bool next(const ExpertTable& tab, int num_experts, int total_items, int n_tiles, int group) {
     if (left > 0) {
@@ -117,7 +117,7 @@ struct TileWalk {
       ++ti.nt;
       return true;
     }
-    item += (int)gridDim.x;
+    item += blocks;
     if (item >= total_items) return false;
     ti.e = upper_bound_expert(tab.prefix, num_experts, item);
     const int i = item - tab.prefix[ti.e];
@@ -136,14 +136,17 @@ struct TileWalk {
   }
 };
 
+// One CTA of shape S: `block` of the `blocks` CTAs that serve the experts with min_rows <= rows <= max_rows.  The tensor
+// maps are the kernel's __grid_constant__ parameters.
 template <typename OutT, class S>
-__global__ void __launch_bounds__(S::THREADS, 1)
-fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
-                                const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
-                                const __grid_constant__ CUtensorMap map_x128, const float* __restrict__ scales_a,
-                                const float* __restrict__ scales_b, OutT* __restrict__ d,
-                                const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
-                                int num_experts, int n, int k, int min_rows, int max_rows, int wait_at_start, int group) {
+__device__ __forceinline__ void blockwise_cta(const CUtensorMap& map_w, const CUtensorMap& map_x16,
+                                              const CUtensorMap& map_x32, const CUtensorMap& map_x64,
+                                              const CUtensorMap& map_x128, const float* __restrict__ scales_a,
+                                              const float* __restrict__ scales_b, OutT* __restrict__ d,
+                                              const int* __restrict__ problem_sizes,
+                                              const int* __restrict__ expert_offsets, int num_experts, int n, int k,
+                                              int min_rows, int max_rows, int wait_at_start, int group, int block,
+                                              int blocks) {
   constexpr int TOK = S::TOK_TILE;
   constexpr int STAGES = S::STAGES;
   constexpr int NCH = S::NCH;
@@ -217,7 +220,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      TileWalk<TOK> walk;
+      TileWalk<TOK> walk(block, blocks);
       while (ok && walk.next(tab, num_experts, total_items, n_tiles, group)) {
         const TileInfo& ti = walk.ti;
         const CUtensorMap* xm = ti.n_mma <= 16 ? &map_x16 : ti.n_mma <= 32 ? &map_x32 : ti.n_mma <= 64 ? &map_x64 : &map_x128;
@@ -246,7 +249,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
       const int mine = warp - 1;
       int g = 0;
       bool ok = true;
-      TileWalk<TOK> walk;
+      TileWalk<TOK> walk(block, blocks);
       while (ok && walk.next(tab, num_experts, total_items, n_tiles, group)) {
         const TileInfo& ti = walk.ti;
         const uint32_t idesc = ptx::make_idesc_f8(TILE_N, ti.n_mma);
@@ -282,7 +285,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
     const int mine = warp - 3;
     int c = 0;
     bool ok = true;
-    TileWalk<TOK> walk;
+    TileWalk<TOK> walk(block, blocks);
     while (ok && walk.next(tab, num_experts, total_items, n_tiles, group)) {
       const int chunks_in_tile = (kt_count + CH_KT - 1) / CH_KT;
       // this warp's chunks of the tile: c, c+1, .. with (c & 1) == mine
@@ -343,7 +346,7 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
     bool alive = true;
     uint32_t turn_ph = 0;
     int tile_index = 0;
-    TileWalk<TOK> walk;
+    TileWalk<TOK> walk(block, blocks);
     while (alive && walk.next(tab, num_experts, total_items, n_tiles, group)) {
       const int my_index = tile_index++;
       if ((my_index & (S::GROUPS - 1)) != egroup) {   // the other group's tile
@@ -446,64 +449,162 @@ fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const
 }
 
 template <typename OutT, class S>
-int launch(const void* a, const void* b, const float* sa, const float* sb, void* d, const int32_t* ps,
-           const int32_t* eo, int num_experts, int64_t num_rows, int n, int k, int min_rows, int max_rows,
-           bool first_of_call, cudaStream_t stream) {
-  DeviceInfo info;
-  int rc = get_device_info(&info);
-  if (rc != ES_B200_OK) return rc;
+__global__ void __launch_bounds__(S::THREADS, 1)
+fp8_blockwise_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
+                                const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
+                                const __grid_constant__ CUtensorMap map_x128, const float* __restrict__ scales_a,
+                                const float* __restrict__ scales_b, OutT* __restrict__ d,
+                                const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
+                                int num_experts, int n, int k, int min_rows, int max_rows, int wait_at_start, int group) {
+  blockwise_cta<OutT, S>(map_w, map_x16, map_x32, map_x64, map_x128, scales_a, scales_b, d, problem_sizes, expert_offsets,
+                         num_experts, n, k, min_rows, max_rows, wait_at_start, group, (int)blockIdx.x, (int)gridDim.x);
+}
 
-  CUtensorMap map_w, map_x[4];
-  rc = make_tensormap_u8_sw128(&map_w, b, (uint64_t)num_experts * n, (uint64_t)k, TILE_N);
+// The 64-token and the 128-token shape in one launch (both run 20 warps): CTAs [0, small_ctas) serve the experts with
+// 33..64 rows, the others those with 65 rows and more.  The hardware starts CTAs in index order, so the second shape
+// takes the SMs as the first runs out of items — what two chained launches did, for one launch (and, when a bucket is
+// empty, one pass of empty CTAs over every SM) less per call.
+template <typename OutT>
+__global__ void __launch_bounds__(ShapeSmall::THREADS, 1)
+fp8_blockwise_two_shapes_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x16,
+                                const __grid_constant__ CUtensorMap map_x32, const __grid_constant__ CUtensorMap map_x64,
+                                const __grid_constant__ CUtensorMap map_x128, const float* __restrict__ scales_a,
+                                const float* __restrict__ scales_b, OutT* __restrict__ d,
+                                const int* __restrict__ problem_sizes, const int* __restrict__ expert_offsets,
+                                int num_experts, int n, int k, int small_ctas, int wait_at_start, int group) {
+  static_assert(ShapeSmall::THREADS == ShapeFull::THREADS, "the two shapes share one block size");
+  if ((int)blockIdx.x < small_ctas)
+    blockwise_cta<OutT, ShapeSmall>(map_w, map_x16, map_x32, map_x64, map_x128, scales_a, scales_b, d, problem_sizes,
+                                    expert_offsets, num_experts, n, k, 33, 64, wait_at_start, group, (int)blockIdx.x,
+                                    small_ctas);
+  else
+    blockwise_cta<OutT, ShapeFull>(map_w, map_x16, map_x32, map_x64, map_x128, scales_a, scales_b, d, problem_sizes,
+                                   expert_offsets, num_experts, n, k, 65, 0x7fffffff, wait_at_start, group,
+                                   (int)blockIdx.x - small_ctas, (int)gridDim.x - small_ctas);
+}
+
+struct LaunchArgs {
+  const void* a;
+  const void* b;
+  const float* sa;
+  const float* sb;
+  void* d;
+  const int32_t* ps;
+  const int32_t* eo;
+  int num_experts;
+  int64_t num_rows;
+  int n, k;
+  cudaStream_t stream;
+};
+
+// weight tiles per work item: the per-item work of every role (decode) is spread over ~8 K blocks
+static int tiles_per_item(int k) {
+  const int kt_count = k / TILE_K;
+  const int group = (8 + kt_count - 1) / kt_count;
+  return group < 1 ? 1 : group;
+}
+
+static int make_maps(const LaunchArgs& c, CUtensorMap* map_w, CUtensorMap (&map_x)[4]) {
+  int rc = make_tensormap_u8_sw128(map_w, c.b, (uint64_t)c.num_experts * c.n, (uint64_t)c.k, TILE_N);
   if (rc != ES_B200_OK) return rc;
   const uint32_t boxes[4] = {16, 32, 64, 128};
   for (int i = 0; i < 4; ++i) {
-    rc = make_tensormap_u8_sw128(&map_x[i], a, (uint64_t)num_rows, (uint64_t)k, boxes[i]);
+    rc = make_tensormap_u8_sw128(&map_x[i], c.a, (uint64_t)c.num_rows, (uint64_t)c.k, boxes[i]);
     if (rc != ES_B200_OK) return rc;
   }
-  auto kernel = fp8_blockwise_grouped_mm_kernel<OutT, S>;
-  static bool configured[64] = {false};
+  return ES_B200_OK;
+}
+
+// CTAs for one shape: one per SM, fewer when the host-known upper bound of its item count is smaller
+template <class S>
+static int ctas_for(const LaunchArgs& c, int group, int sm_count) {
+  const int64_t max_items = ((c.num_rows + S::TOK_TILE - 1) / S::TOK_TILE + c.num_experts) *
+                            (int64_t)((c.n / TILE_N + group - 1) / group);
+  return (int)(max_items < sm_count ? max_items : sm_count);
+}
+
+template <typename Kernel>
+static int configure(Kernel kernel, size_t smem_bytes, bool (&configured)[64]) {
   int dev = 0;
   ES_CUDA_TRY(cudaGetDevice(&dev));
   if (!configured[dev & 63]) {
-    ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES));
+    ES_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     configured[dev & 63] = true;
   }
-  // weight tiles per work item: the per-item work of every role (decode) is spread over ~8 K blocks
-  const int kt_count = k / TILE_K;
-  static const int group_blocks = getenv("ES_DBG_GROUP_BLOCKS") ? atoi(getenv("ES_DBG_GROUP_BLOCKS")) : 8;   // DEBUG
-  int group = (group_blocks + kt_count - 1) / kt_count;
-  if (group < 1) group = 1;
-  const int64_t max_items = ((num_rows + S::TOK_TILE - 1) / S::TOK_TILE + num_experts) *
-                            (int64_t)((n / TILE_N + group - 1) / group);
-  const int grid = (int)(max_items < info.sm_count ? max_items : info.sm_count);
+  return ES_B200_OK;
+}
 
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(S::THREADS);
-  cfg.dynamicSmemBytes = S::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+static void pdl_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int grid, int threads, size_t smem,
+                       cudaStream_t stream) {
+  *cfg = {};
+  cfg->gridDim = dim3(grid);
+  cfg->blockDim = dim3(threads);
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = stream;
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], sa, sb,
-                                 static_cast<OutT*>(d), ps, eo, num_experts, n, k, min_rows, max_rows,
-                                 first_of_call ? 1 : 0, group));
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
+
+// the <= 32-row shape (13 warps), always the first kernel of a call
+template <typename OutT>
+int launch_tiny(const LaunchArgs& c) {
+  using S = ShapeTiny;
+  DeviceInfo info;
+  int rc = get_device_info(&info);
+  if (rc != ES_B200_OK) return rc;
+  CUtensorMap map_w, map_x[4];
+  rc = make_maps(c, &map_w, map_x);
+  if (rc != ES_B200_OK) return rc;
+  auto kernel = fp8_blockwise_grouped_mm_kernel<OutT, S>;
+  static bool configured[64] = {false};
+  rc = configure(kernel, S::SMEM_BYTES, configured);
+  if (rc != ES_B200_OK) return rc;
+  const int group = tiles_per_item(c.k);
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[1];
+  pdl_config(&cfg, attr, ctas_for<S>(c, group, info.sm_count), S::THREADS, S::SMEM_BYTES, c.stream);
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], c.sa, c.sb,
+                                 static_cast<OutT*>(c.d), c.ps, c.eo, c.num_experts, c.n, c.k, 1, 32, 1, group));
+  return ES_B200_OK;
+}
+
+// the 33..64-row and the >= 65-row shapes in one launch; want_full = false leaves the first alone
+template <typename OutT>
+int launch_small_and_full(const LaunchArgs& c, bool want_full) {
+  DeviceInfo info;
+  int rc = get_device_info(&info);
+  if (rc != ES_B200_OK) return rc;
+  CUtensorMap map_w, map_x[4];
+  rc = make_maps(c, &map_w, map_x);
+  if (rc != ES_B200_OK) return rc;
+  auto kernel = fp8_blockwise_two_shapes_kernel<OutT>;
+  constexpr size_t SMEM = ShapeSmall::SMEM_BYTES > ShapeFull::SMEM_BYTES ? ShapeSmall::SMEM_BYTES : ShapeFull::SMEM_BYTES;
+  static bool configured[64] = {false};
+  rc = configure(kernel, SMEM, configured);
+  if (rc != ES_B200_OK) return rc;
+  const int group = tiles_per_item(c.k);
+  const int small_ctas = ctas_for<ShapeSmall>(c, group, info.sm_count);
+  const int full_ctas = want_full ? ctas_for<ShapeFull>(c, group, info.sm_count) : 0;
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute attr[1];
+  pdl_config(&cfg, attr, small_ctas + full_ctas, ShapeSmall::THREADS, SMEM, c.stream);
+  ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], c.sa, c.sb,
+                                 static_cast<OutT*>(c.d), c.ps, c.eo, c.num_experts, c.n, c.k, small_ctas, 0, group));
   return ES_B200_OK;
 }
 
 template <typename OutT>
 int launch_buckets(const void* a, const void* b, const float* sa, const float* sb, void* d, const int32_t* ps,
                    const int32_t* eo, int num_experts, int64_t num_rows, int n, int k, cudaStream_t stream) {
-  // One kernel per row-count bucket, back to back with programmatic dependent launch; each filters the experts in
-  // its own scan.  A bucket that even the host-known upper bound of rows per expert cannot reach is not launched.
-  int rc = launch<OutT, ShapeTiny>(a, b, sa, sb, d, ps, eo, num_experts, num_rows, n, k, 1, 32, true, stream);
+  // The <= 32-row shape first, then the two larger shapes in one launch, chained with programmatic dependent launch;
+  // every CTA filters the experts in its own scan.  A bucket that even the host-known upper bound of rows per expert
+  // cannot reach gets no CTAs.
+  const LaunchArgs c = {a, b, sa, sb, d, ps, eo, num_experts, num_rows, n, k, stream};
+  int rc = launch_tiny<OutT>(c);
   if (rc != ES_B200_OK || num_rows <= 32) return rc;
-  rc = launch<OutT, ShapeSmall>(a, b, sa, sb, d, ps, eo, num_experts, num_rows, n, k, 33, 64, false, stream);
-  if (rc != ES_B200_OK || num_rows <= 64) return rc;
-  return launch<OutT, ShapeFull>(a, b, sa, sb, d, ps, eo, num_experts, num_rows, n, k, 65, 0x7fffffff, false, stream);
+  return launch_small_and_full<OutT>(c, num_rows > 64);
 }
 
 int read_and_clear_status(uint32_t* out) {
