@@ -87,8 +87,15 @@ template <typename OutT, int PARTS, class Release>
 __device__ __forceinline__ void drain_partial_sums(uint32_t taddr, uint32_t part_stride, int parts_written, int n_cols,
                                                    int valid, OutT* stage_warp, OutT* dst, int64_t ld, int lane,
                                                    Release release, const RowScatter& scatter, int64_t first_row,
-                                                   int col_off, uint32_t* status, bool direct_stores) {
-  for (int c = 0; c < n_cols; c += 32) {
+                                                   int col_off, uint32_t* status, bool direct_stores,
+                                                   int first_col = 0, int col_stride = 32) {
+  // (a warp that shares its lane quadrant with another takes the 32-column chunks first_col, first_col + col_stride,
+  // ...; one without a chunk in this tile only hands the accumulator back)
+  if (first_col >= n_cols) {
+    release();
+    return;
+  }
+  for (int c = first_col; c < n_cols; c += col_stride) {
     OutT* dest = nullptr;
     if (scatter.meta != nullptr)
       dest = scatter_row_ptr<OutT>(scatter, first_row + c + lane, c + lane < valid, ld, col_off, status);
@@ -115,7 +122,7 @@ __device__ __forceinline__ void drain_partial_sums(uint32_t taddr, uint32_t part
         for (int i = 0; i < 16; ++i) acc[h * 16 + i] = 0u;
       }
     }
-    if (c + 32 >= n_cols) release();
+    if (c + col_stride >= n_cols) release();
     if (direct_stores && scatter.meta == nullptr) {
       // dense output without shared memory: a warp-wide 2-byte store writes the 64 contiguous bytes of one token row.
       // The caller asks for it when K is long (the output is a small part of the call's bytes): no store -> sync ->

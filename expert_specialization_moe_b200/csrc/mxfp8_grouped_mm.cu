@@ -72,7 +72,7 @@ constexpr uint32_t SF_SLOT_COLS = 8;    // per ring slot: 4 columns of weight sc
 
 // A streaming shape: experts with at most TOK_TILE rows (ONE token tile per expert: the tile's token scales are then
 // exactly one 128-row atom), STAGES ring slots, LANES MMA-issuing threads = partial accumulators.
-template <int TOK_TILE_, int STAGES_, int LANES_, bool SECOND_LOAD_PATH_>
+template <int TOK_TILE_, int STAGES_, int LANES_, bool SECOND_LOAD_PATH_, bool SECOND_EPILOGUE_>
 struct Shape {
   static constexpr int TOK_TILE = TOK_TILE_;     // token rows per tile (tcgen05.mma N, runtime multiple of 16)
   static constexpr int STAGES = STAGES_;
@@ -81,6 +81,12 @@ struct Shape {
   // loader threads copy as many token bytes, L2 hits, as weight bytes: 48 vs 52 GB/s per SM) but inside a call, next to
   // the other kernels, the call is faster with it (reference-distribution workload at 32 experts: 0.1938 vs 0.1967 ms)
   static constexpr bool SECOND_LOAD_PATH = SECOND_LOAD_PATH_;
+  // With few K steps per tile the four epilogue warps set the pace of a tile of many tokens (partial sums and the store
+  // of four 32-token chunks take ~10000 cycles, the loads of three K steps ~1500).  The shape can then run the four
+  // loader warps as a second epilogue group instead (every ring slot by TMA; the two groups take alternate chunks).
+  // Needs four more 2 KB store tiles, which the 32-token shape has no room for and, with its single chunk, no use for.
+  static constexpr bool SECOND_EPILOGUE = SECOND_EPILOGUE_;
+  static constexpr int EPILOGUE_TILES = SECOND_EPILOGUE ? 8 : 4;
   static constexpr int X_BYTES = TOK_TILE * TILE_K;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + 2 * SF_BYTES;   // W | X | weight scales | token scales
   static constexpr uint32_t ACC_COLS = LANES * TOK_TILE;                 // one accumulator buffer: LANES partials
@@ -89,8 +95,8 @@ struct Shape {
   static_assert(TOK_TILE % 16 == 0 && TOK_TILE <= 128 && (LANES == 1 || LANES == 2 || LANES == 4), "tile shape");
   static_assert(SF_COL0 + STAGES * SF_SLOT_COLS <= TMEM_COLS, "TMEM budget");
 };
-using ShapeTiny = Shape<32, 10, 4, true>;   // 21 KB slots; TMEM: 2 x 4 x 32 accumulator columns + 80 scale columns
-using ShapeMid = Shape<112, 6, 2, true>;    // 31 KB slots; TMEM: 2 x 2 x 112 accumulator columns + 48 scale columns
+using ShapeTiny = Shape<32, 10, 4, true, false>;   // 21 KB slots; TMEM: 2 x 4 x 32 accumulator columns + 80 scale columns
+using ShapeMid = Shape<112, 6, 2, true, true>;   // 31 KB slots; TMEM: 2 x 2 x 112 accumulator columns + 48 scale columns
 
 // CTAs of the 112-token shape in front of the 32-token shape's (tunable mm_stream_mid_lead_ctas < 0).  Measured in one
 // process, bursts of 20 calls, on the reference benchmark's row distribution: n = 512, E = 256: 0.1980 ms with 0,
@@ -106,7 +112,7 @@ struct SharedCtl {
   uint64_t empty[MAX_STAGES];           // 1 arrival: the commit of the MMA lane that owns the K step
   uint64_t sf_ready[MAX_STAGES];        // 2 arrivals: both scale atoms of the slot are in its TMEM columns
   uint64_t tmem_full[2];                // LANES arrivals: every MMA lane's share of the tile is complete
-  uint64_t tmem_empty[2];               // 4 arrivals: the epilogue warps have read the buffer
+  uint64_t tmem_empty[2];               // 4 (8 with the second group) arrivals: the epilogue warps have read the buffer
   uint64_t q_full[QUEUE_DEPTH];         // 1 arrival: the producer lane has written q_tile[slot]
   uint64_t q_empty[QUEUE_DEPTH];        // every consuming role has read it
   int q_tile[QUEUE_DEPTH];              // tile index, or -1: no more work
@@ -118,7 +124,8 @@ struct SharedCtl {
 
 template <class S>
 constexpr size_t smem_bytes() {
-  return 1024 /*alignment slack*/ + (size_t)S::STAGES * S::STAGE_BYTES + 4 * EPI_STAGE_BYTES_PER_WARP + sizeof(SharedCtl);
+  return 1024 /*alignment slack*/ + (size_t)S::STAGES * S::STAGE_BYTES + S::EPILOGUE_TILES * EPI_STAGE_BYTES_PER_WARP +
+         sizeof(SharedCtl);
 }
 
 __device__ uint32_t g_status = 0;   // sticky error bits of the grouped GEMM kernels (bounded waits that gave up)
@@ -199,7 +206,11 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
                                                const CUtensorMap& map_xt, const CUtensorMap& map_sfx,
                                                const CUtensorMap& map_sfw, const KernelArgs& args,
                                                const RowScatter& scatter, int min_rows, int max_rows, int bucket,
-                                               int use_lsu, int block, int blocks) {
+                                               int load_mode, int block, int blocks) {
+  // load_mode 0: every ring slot by TMA; 1: odd slots by cp.async from warps 7..10; 2: every slot by TMA and warps 7..10
+  // are a second epilogue group (shapes with SECOND_EPILOGUE only)
+  const bool use_lsu = load_mode == 1;
+  const bool epi2 = S::SECOND_EPILOGUE && load_mode == 2;
   const uint8_t* __restrict__ a_codes = args.a_codes;
   const uint8_t* __restrict__ w_codes = args.w_codes;
   const uint8_t* __restrict__ sf_tokens = args.sf_tokens;
@@ -222,8 +233,8 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
   constexpr int LANES = S::LANES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 4 x 2 KB, one per epilogue warp
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + 4 * EPI_STAGE_BYTES_PER_WARP);
+  uint8_t* epi_stage = smem + (size_t)STAGES * STAGE_BYTES;      // 2 KB per epilogue warp
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(epi_stage + S::EPILOGUE_TILES * EPI_STAGE_BYTES_PER_WARP);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -235,12 +246,13 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&ctl->tmem_full[a], LANES);
-      ptx::mbar_init(&ctl->tmem_empty[a], 4);
+      ptx::mbar_init(&ctl->tmem_empty[a], epi2 ? 8 : 4);
     }
     for (int q = 0; q < QUEUE_DEPTH; ++q) {
       ptx::mbar_init(&ctl->q_full[q], 1);
-      // readers: LANES MMA lanes, 2 copy lanes, 4 epilogue warps, and the 4 loader warps when they run
-      ptx::mbar_init(&ctl->q_empty[q], LANES + 2 + 4 + (use_lsu ? LOADER_THREADS / 32 : 0));
+      // readers: LANES MMA lanes, 2 copy lanes, 4 epilogue warps, and warps 7..10 when they run (as loaders or as the
+      // second epilogue group)
+      ptx::mbar_init(&ctl->q_empty[q], LANES + 2 + 4 + ((use_lsu || epi2) ? LOADER_THREADS / 32 : 0));
     }
     ctl->abort_flag = 0;
     ptx::fence_mbar_init();
@@ -295,6 +307,46 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
   const int kt_count = k / TILE_K;
   volatile int* abort_flag = &ctl->abort_flag;
   const int mma_lane = warp == 1 ? 0 : (warp >= MMA_WARP1 && warp < MMA_WARP1 + MAX_LANES - 1) ? warp - MMA_WARP1 + 1 : -1;
+
+  // ------------------------------------------------------------------ epilogue: warps 2..5, and warps 7..10 as a second
+  // group when the shape runs that way; a group's warp takes the 32-token chunks first_col, first_col + col_stride, ...
+  auto run_epilogue = [&](OutT* stage_warp, int first_col, int col_stride) {
+    const int quad = warp & 3;   // TMEM lane quadrant this warp may access
+    QueueReader q;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    while (ok) {
+      int t;
+      if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
+      if (t < 0) break;
+      const TileInfo ti = decode_tile(t, tab, num_experts, n_tiles, group);
+      for (int sub = 0; ok && sub < ti.n_sub; ++sub) {
+      const int nt = ti.nt + sub;
+      const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * S::ACC_COLS + ((uint32_t)(quad * 32) << 16);
+      OutT* dst = d + (int64_t)ti.row0 * n + (nt * TILE_N + quad * 32);
+      drain_partial_sums<OutT, LANES>(
+          taddr, TOK_TILE, kt_count < LANES ? kt_count : LANES, ti.n_mma, ti.valid,
+          stage_warp, dst, n, lane,
+          [&] {
+            // all of this warp's accumulator reads are done: hand the buffer back to the MMA lanes
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+          },
+          scatter, ti.row0, nt * TILE_N + quad * 32, &g_status, kt_count >= 8, first_col, col_stride);
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1u;
+      }   // weight tiles of the item
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicOr(&g_status, ERR_EPILOGUE);
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer (whole warp walks the work list)
@@ -454,7 +506,9 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
     // waits for its own copies and keeps as many slots in flight as the ring has free.  The consumers of a cp.async
     // slot (MMA lanes, copy lanes) issue a proxy fence after their wait: the data was written through the generic
     // proxy and is read by tcgen05 through the async proxy.
-    if (use_lsu) {
+    if (epi2) {
+      run_epilogue(reinterpret_cast<OutT*>(epi_stage) + (4 + warp - LOADER_WARP0) * 1024, 32, 64);
+    } else if (use_lsu) {
       const int lt = threadIdx.x - LOADER_WARP0 * 32;        // 0..127
       const int c16 = lt & 7, r0 = lt >> 3;                   // this thread's 16-byte column and first row
       QueueReader q;
@@ -510,42 +564,7 @@ __device__ __forceinline__ void grouped_mm_cta(const CUtensorMap& map_w, const C
       }
     }
   } else if (warp >= 2 && warp <= 5) {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quad = warp & 3;   // TMEM lane quadrant this warp may access
-    QueueReader q;
-    int acc = 0;
-    uint32_t acc_ph = 0;
-    bool ok = true;
-    while (ok) {
-      int t;
-      if (!q.next<true>(ctl, abort_flag, lane, &t)) { ok = false; break; }
-      if (t < 0) break;
-      const TileInfo ti = decode_tile(t, tab, num_experts, n_tiles, group);
-      for (int sub = 0; ok && sub < ti.n_sub; ++sub) {
-      const int nt = ti.nt + sub;
-      const bool got = ptx::mbar_wait(&ctl->tmem_full[acc], acc_ph, abort_flag);
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-      ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + acc * S::ACC_COLS + ((uint32_t)(quad * 32) << 16);
-      OutT* dst = d + (int64_t)ti.row0 * n + (nt * TILE_N + quad * 32);
-      drain_partial_sums<OutT, LANES>(
-          taddr, TOK_TILE, kt_count < LANES ? kt_count : LANES, ti.n_mma, ti.valid,
-          reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, dst, n, lane,
-          [&] {
-            // all of this warp's accumulator reads are done: hand the buffer back to the MMA lanes
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
-          },
-          scatter, ti.row0, nt * TILE_N + quad * 32, &g_status, kt_count >= 8);
-      acc ^= 1;
-      if (acc == 0) acc_ph ^= 1u;
-      }   // weight tiles of the item
-    }
-    if (!ok && lane == 0) {
-      *abort_flag = 1;
-      atomicOr(&g_status, ERR_EPILOGUE);
-    }
+    run_epilogue(reinterpret_cast<OutT*>(epi_stage) + (warp - 2) * 1024, 0, epi2 ? 64 : 32);
   }
   // (warps of MMA lanes the shape does not use fall through)
 
@@ -572,15 +591,15 @@ mxfp8_grouped_mm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                         const __grid_constant__ CUtensorMap map_x112, const __grid_constant__ CUtensorMap map_sfx,
                         const __grid_constant__ CUtensorMap map_sfw, const __grid_constant__ KernelArgs args,
                         const __grid_constant__ RowScatter scatter, int tiny_ctas, int mid_lead, int split_rows,
-                        int max_rows, int use_lsu_tiny, int use_lsu_mid) {
+                        int max_rows, int load_mode_tiny, int load_mode_mid) {
   const int mid_ctas = (int)gridDim.x - tiny_ctas;
   const int b = (int)blockIdx.x;
   if (b >= mid_lead && b < mid_lead + tiny_ctas)
     grouped_mm_cta<OutT, ShapeTiny>(map_w, map_x16, map_x32, map_x64, map_x32, map_sfx, map_sfw, args, scatter, 1,
-                                    split_rows, 0, use_lsu_tiny, b - mid_lead, tiny_ctas);
+                                    split_rows, 0, load_mode_tiny, b - mid_lead, tiny_ctas);
   else
     grouped_mm_cta<OutT, ShapeMid>(map_w, map_x16, map_x32, map_x64, map_x112, map_sfx, map_sfw, args, scatter,
-                                   split_rows + 1, max_rows, 1, use_lsu_mid, b < mid_lead ? b : b - tiny_ctas, mid_ctas);
+                                   split_rows + 1, max_rows, 1, load_mode_mid, b < mid_lead ? b : b - tiny_ctas, mid_ctas);
 }
 
 // earlier_ctas: in/out — CTAs launched so far by this call; the last kernel of the call waits for that many reports.
@@ -655,7 +674,8 @@ int launch_streaming(const CallArgs& c, int tiny_max, int mid_max, bool want_tin
                      first_of_call ? 1 : 0, group, c.counters, last_of_call ? 1 : 0, *earlier_ctas};
   ES_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, map_w, map_x[0], map_x[1], map_x[2], map_x[3], map_sfx, map_sfw, args,
                                  *c.scatter, first_ctas, mid_lead, tiny_max, mid_max,
-                                 (ShapeTiny::SECOND_LOAD_PATH && lsu) ? 1 : 0, (ShapeMid::SECOND_LOAD_PATH && lsu) ? 1 : 0));
+                                 (ShapeTiny::SECOND_LOAD_PATH && lsu) ? 1 : 0,
+                                 (ShapeMid::SECOND_EPILOGUE && kt_count < 8) ? 2 : (ShapeMid::SECOND_LOAD_PATH && lsu) ? 1 : 0));
   *earlier_ctas += (uint32_t)grid;
   return ES_B200_OK;
 }
