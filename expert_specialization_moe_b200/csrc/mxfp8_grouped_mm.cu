@@ -35,13 +35,16 @@
 //               the MMAs of the next tile
 //   warps 6, 14 scale copies, one lane each: the slot's weight / token scale atom smem -> the slot's TMEM columns
 //               (tcgen05.cp), tcgen05.commit to the slot's sf_ready barrier
-//   warps 7-10  second load path: the odd ring slots by cp.async
+//   warps 7-10  second load path: the odd ring slots by cp.async — or, for the 112-token shape when K is short, a
+//               second epilogue group (every slot is then filled by TMA and the two groups take alternate 32-token
+//               chunks of a tile)
 //
-// Work list: tiles (expert, weight tile of 128) found with a per-CTA prefix scan over the problem sizes (device
-// resident: no host round trip).  The producer takes tile indices from the bucket's work counter in the caller's
-// scratch (atomicAdd; round-robin over the grid when the caller gave no scratch) and hands each one to the other
-// roles through a small shared-memory queue, so a CTA that starts late — behind another kernel of the same call —
-// just takes what is left.
+// Work list: items (expert, 1..8 consecutive weight tiles of 128 — one tile when K is long, several when it is short, so
+// that an item spans ~16 K steps) found with a per-CTA prefix scan over the problem sizes (device resident: no host
+// round trip).  The producer takes item indices from the bucket's work counter in the caller's scratch (atomicAdd;
+// round-robin over the shape's CTAs when the caller gave no scratch) and hands each one to the other roles through a
+// small shared-memory queue, so a CTA that starts late — behind other CTAs of the same call — just takes what is left.
+// Both shapes run in ONE launch (mxfp8_grouped_mm_kernel below picks the shape from the CTA index).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cstdlib>
