@@ -31,8 +31,9 @@
 //   warp 1, 11-13  MMA issue, one lane each (as many as the shape has LANES): 4 x tcgen05.mma (K=32 each) per own K
 //               step, tcgen05.commit to free the slot / publish the accumulator; warp 1 also owns the TMEM allocation
 //   warps 2-5   epilogue: tcgen05.ld of the partial accumulators (lane = output column, column = token), fp32 sum,
-//               -> bf16/fp16 -> global through a shared-memory transpose, 128-bit stores; double-buffered against
-//               the MMAs of the next tile
+//               -> bf16/fp16 -> global: a 2-byte store per lane and token row when K is long (no shared memory), a
+//               shared-memory transpose and 128-bit stores when K is short or the output is scattered;
+//               double-buffered against the MMAs of the next tile
 //   warps 6, 14 scale copies, one lane each: the slot's weight / token scale atom smem -> the slot's TMEM columns
 //               (tcgen05.cp), tcgen05.commit to the slot's sf_ready barrier
 //   warps 7-10  second load path: the odd ring slots by cp.async — or, for the 112-token shape when K is short, a
