@@ -16,8 +16,8 @@
 //   warps 1, 2 MMA issue, one lane each: warp 1 (which also owns the TMEM allocation) takes the even K blocks, warp 2
 //              the odd ones — consecutive K blocks go to different partial buffers, and a tcgen05.mma costs its
 //              issuing thread ~90 cycles against 64 cycles of tensor time for a 128 x 128 x 32 MMA
-//   warps 3(,4) scale loaders (two of them alternate chunks where registers allow): sa[token, kb] * sb[tile, kb] for 8 K blocks at a time, transposed to
-//              [kb][token] in a ring of chunks, so that the epilogue reads one broadcast float4 per 4 tokens and
+//   warps 3(,4) scale loaders (two of them alternate chunks where registers allow): sa[token, kb] * sb[tile, kb] for
+//              8 K blocks at a time, transposed to [kb][token] in a ring of chunks, so that the epilogue reads one broadcast float4 per 4 tokens and
 //              never waits on global memory, whatever K is
 //   then       promotion (partial * scale -> fp32 registers) and output through a per-warp shared-memory transpose:
 //              one set of four warps (the four TMEM lane quadrants) per 32 token columns, so that a warp holds
@@ -101,10 +101,10 @@ struct TileInfo {
 };
 
 // A work item is `group` consecutive weight tiles of one (expert, token tile); CTA `block` of the `blocks` CTAs of its
-// shape takes the items block, block + blocks, ... and every role walks their tiles in the same order.  The item is decoded once (binary
-// search over the item prefix, a division) and the tiles inside it only advance `nt`: with two K blocks per tile
-// (k = 256) every role spent more time per tile finding out what the tile was than working on it (measured: the
-// producer lane and both MMA lanes ~2200 cycles per tile, almost none of it waiting).
+// shape takes the items block, block + blocks, ... and every role walks their tiles in the same order.  The item is
+// decoded once (binary search over the item prefix, a division) and the tiles inside it only advance `nt`: with two
+// K blocks per tile (k = 256) every role spent more time per tile finding out what the tile was than working on it
+// (measured: the producer lane and both MMA lanes ~2200 cycles per tile, almost none of it waiting).
 template <int TOK_TILE>
 struct TileWalk {
   TileInfo ti;

@@ -9,7 +9,8 @@ For every workload and step count the two implementations run INTERLEAVED (ours,
 100 calls start after 1.5 s of idle GPU: the burst regime, as `bench.py --steps 20` in a fresh process); the SM clock is
 sampled with nvidia-smi while each arm runs (groups of 100 calls or more).  One JSON line per measurement: medians of
 ms per call for both arms, their ratio, ms x median SM MHz (what the call costs in SM cycles, comparable across
-power-cap states) and the output agreement.  Never run on more than one GPU: the reference kernel issues cluster-multicast TMA loads.
+power-cap states) and the output agreement.  Never run on more than one GPU: the reference kernel issues
+cluster-multicast TMA loads.
 """
 from __future__ import annotations
 
